@@ -1,0 +1,547 @@
+// LSH cluster assignment: projection onto the random hyperplanes, sign packing, and the
+// compaction of raw bucket codes into dense 1-based ids with per-bucket counts and the
+// bucket permutation the deterministic mean runs over.
+//
+// Projection kernel (the only heavy part: it reads all of X once):
+//   * a CTA walks row tiles of TR rows; X arrives in k-chunks of KC columns through a
+//     two-stage cp.async pipeline into padded shared memory (conflict-free 128-bit reads);
+//   * each thread owns RPT rows and all `bits` accumulators of them, so the n x bits
+//     projection never leaves registers in the fused path; plane values are broadcast
+//     128-bit shared loads shared by the RPT rows;
+//   * every accumulator is the chain p = fma(x[r,k], w[k,h], p), k ascending from +0 --
+//     the order the CPU oracle restates, which makes the sign bits reproducible bit for bit.
+// Compaction sorts (code,row) pairs with a stable radix sort (CUB), so neither a 2^bits
+// histogram nor any atomic is involved and the permutation is deterministic.
+#include <algorithm>
+#include <cub/cub.cuh>
+
+#include "cgnn_plan.h"
+
+namespace cgnn {
+
+static __device__ int g_cluster_status = 0;
+
+int cluster_status(int *out) {
+    int zero = 0;
+    CGNN_CUDA(cudaMemcpyFromSymbol(out, g_cluster_status, sizeof(int)));
+    CGNN_CUDA(cudaMemcpyToSymbol(g_cluster_status, &zero, sizeof(int)));
+    return CGNN_OK;
+}
+
+constexpr int PROJ_THREADS = 128;
+constexpr int KC = 32;        // columns per pipeline stage
+constexpr int XS_STRIDE = 36; // padded row stride of the X stage (elements)
+
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem, int src_bytes) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem),
+                 "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+template <typename T, int HB, int RPT>
+struct ProjSmem {
+    static constexpr int TR = PROJ_THREADS * RPT;
+    T xs[2][TR][XS_STRIDE];
+    T ws[2][KC][HB];
+};
+
+// Stage loader: X[row0 .. row0+TR, k0 .. k0+KC) and planes[k0 .. k0+KC, 0..bits) -> shared,
+// zero-filled outside the matrix.  The vector path needs 16-byte aligned rows.
+template <typename T, int HB, int RPT>
+__device__ __forceinline__ void load_stage(ProjSmem<T, HB, RPT> &sm, int stage, const T *x,
+                                           const T *planes, int64_t n, int64_t width, int bits,
+                                           int64_t row0, int64_t k0, bool vec_ok) {
+    constexpr int TR = PROJ_THREADS * RPT;
+    constexpr int VW = 16 / (int)sizeof(T);
+    constexpr int VPR = KC / VW;  // vectors per row of the stage
+    if (vec_ok) {
+        for (int i = threadIdx.x; i < TR * VPR; i += PROJ_THREADS) {
+            const int r = i / VPR, c = (i % VPR) * VW;
+            const int64_t gr = row0 + r, gk = k0 + c;
+            const bool ok = gr < n && gk < width;  // width % VW == 0 on this path
+            cp_async16(&sm.xs[stage][r][c], ok ? (const void *)(x + gr * width + gk) : (const void *)x,
+                       ok ? 16 : 0);
+        }
+    } else {
+        for (int i = threadIdx.x; i < TR * KC; i += PROJ_THREADS) {
+            const int r = i / KC, c = i % KC;
+            const int64_t gr = row0 + r, gk = k0 + c;
+            sm.xs[stage][r][c] = (gr < n && gk < width) ? x[gr * width + gk] : T(0);
+        }
+    }
+    for (int i = threadIdx.x; i < KC * HB; i += PROJ_THREADS) {
+        const int k = i / HB, h = i % HB;
+        const int64_t gk = k0 + k;
+        sm.ws[stage][k][h] = (gk < width && h < bits) ? planes[gk * bits + h] : T(0);
+    }
+}
+
+template <typename T, int HB, int RPT>
+__global__ void __launch_bounds__(PROJ_THREADS)
+project_kernel(const T *__restrict__ x, const T *__restrict__ planes, int64_t n, int64_t width,
+               int bits, T *__restrict__ proj, int32_t *__restrict__ codes, int vec_ok_i) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    using Smem = ProjSmem<T, HB, RPT>;
+    Smem &sm = *reinterpret_cast<Smem *>(smem_raw);
+    constexpr int TR = PROJ_THREADS * RPT;
+    constexpr int VW = 16 / (int)sizeof(T);
+    using V = Vec<T, VW>;
+    const bool vec_ok = vec_ok_i != 0;
+    const int64_t tiles = (n + TR - 1) / TR;
+    const int64_t nk = (width + KC - 1) / KC;
+    // Stages of this CTA: (tile, k-chunk) pairs, tiles strided by the grid.
+    const int64_t my_tiles = blockIdx.x < tiles ? (tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int64_t stages = my_tiles * nk;
+    if (stages == 0) return;
+
+    T acc[RPT][HB];
+    load_stage<T, HB, RPT>(sm, 0, x, planes, n, width, bits, (int64_t)blockIdx.x * TR, 0, vec_ok);
+    cp_async_commit();
+    for (int64_t s = 0; s < stages; ++s) {
+        const int cur = (int)(s & 1);
+        const int64_t tile = blockIdx.x + (s / nk) * gridDim.x;
+        const int64_t kc = s % nk;
+        if (s + 1 < stages) {
+            const int64_t ntile = blockIdx.x + ((s + 1) / nk) * gridDim.x;
+            load_stage<T, HB, RPT>(sm, cur ^ 1, x, planes, n, width, bits, ntile * TR,
+                                   ((s + 1) % nk) * KC, vec_ok);
+        }
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        if (kc == 0) {
+#pragma unroll
+            for (int i = 0; i < RPT; ++i)
+#pragma unroll
+                for (int h = 0; h < HB; ++h) acc[i][h] = T(0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < KC; kk += VW) {
+            V xv[RPT];
+#pragma unroll
+            for (int i = 0; i < RPT; ++i)
+                xv[i] = *reinterpret_cast<const V *>(&sm.xs[cur][threadIdx.x + i * PROJ_THREADS][kk]);
+#pragma unroll
+            for (int q = 0; q < VW; ++q) {
+#pragma unroll
+                for (int h4 = 0; h4 < HB; h4 += VW) {
+                    const V w = *reinterpret_cast<const V *>(&sm.ws[cur][kk + q][h4]);
+#pragma unroll
+                    for (int j = 0; j < VW; ++j)
+#pragma unroll
+                        for (int i = 0; i < RPT; ++i)
+                            acc[i][h4 + j] = fma(xv[i].v[q], w.v[j], acc[i][h4 + j]);
+                }
+            }
+        }
+        if (kc == nk - 1) {
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) {
+                const int64_t row = tile * TR + threadIdx.x + i * PROJ_THREADS;
+                if (row < n) {
+                    if (proj) {
+#pragma unroll
+                        for (int h = 0; h < HB; ++h)
+                            if (h < bits) proj[row * bits + h] = acc[i][h];
+                    }
+                    if (codes) {
+                        int32_t id = 0;
+#pragma unroll
+                        for (int h = 0; h < HB; ++h)
+                            if (h < bits) id = (id << 1) | (acc[i][h] > T(0) ? 1 : 0);
+                        codes[row] = id;
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <typename T, int HB>
+static int launch_project(const T *x, const T *planes, int64_t n, int64_t width, int bits,
+                          T *proj, int32_t *codes, cudaStream_t stream) {
+    constexpr int RPT = sizeof(T) == 4 ? 2 : 1;
+    using Smem = ProjSmem<T, HB, RPT>;
+    constexpr int TR = PROJ_THREADS * RPT;
+    constexpr int VW = 16 / (int)sizeof(T);
+    const size_t smem = sizeof(Smem);
+    auto kernel = project_kernel<T, HB, RPT>;
+    CGNN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int64_t tiles = ceil_div(n, TR);
+    const int64_t grid = std::min<int64_t>(tiles, 148 * 2);
+    const bool vec_ok = width % VW == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    kernel<<<(unsigned)grid, PROJ_THREADS, smem, stream>>>(x, planes, n, width, bits, proj, codes,
+                                                          vec_ok ? 1 : 0);
+    CGNN_LAUNCH_CHECK();
+    return CGNN_OK;
+}
+
+template <typename T>
+static int project_typed(const T *x, const T *planes, int64_t n, int64_t width, int bits, T *proj,
+                         int32_t *codes, cudaStream_t stream) {
+    if (n == 0) return CGNN_OK;
+    if (bits == 0) {
+        if (codes) CGNN_CUDA(cudaMemsetAsync(codes, 0, sizeof(int32_t) * (size_t)n, stream));
+        return CGNN_OK;
+    }
+    if (width == 0) {
+        if (codes) CGNN_CUDA(cudaMemsetAsync(codes, 0, sizeof(int32_t) * (size_t)n, stream));
+        if (proj) CGNN_CUDA(cudaMemsetAsync(proj, 0, sizeof(T) * (size_t)n * (size_t)bits, stream));
+        return CGNN_OK;
+    }
+    switch ((bits + 3) / 4) {
+        case 1: return launch_project<T, 4>(x, planes, n, width, bits, proj, codes, stream);
+        case 2: return launch_project<T, 8>(x, planes, n, width, bits, proj, codes, stream);
+        case 3: return launch_project<T, 12>(x, planes, n, width, bits, proj, codes, stream);
+        case 4: return launch_project<T, 16>(x, planes, n, width, bits, proj, codes, stream);
+        case 5: return launch_project<T, 20>(x, planes, n, width, bits, proj, codes, stream);
+        case 6: return launch_project<T, 24>(x, planes, n, width, bits, proj, codes, stream);
+        case 7: return launch_project<T, 28>(x, planes, n, width, bits, proj, codes, stream);
+        default: return launch_project<T, 32>(x, planes, n, width, bits, proj, codes, stream);
+    }
+}
+
+static int project(int dtype, const void *x, const void *planes, int64_t n, int64_t width, int bits,
+                   void *proj, int32_t *codes, cudaStream_t stream) {
+    CGNN_REQUIRE(dtype == CGNN_F32 || dtype == CGNN_F64, "cluster: unknown dtype %d", dtype);
+    CGNN_REQUIRE(bits >= 0 && bits <= 30, "cluster: hash bits must be in [0,30]");
+    CGNN_REQUIRE(n >= 0 && n <= 0x7fffffffll, "cluster: node count exceeds int32 capacity");
+    CGNN_REQUIRE(width >= 0, "cluster: negative width");
+    if (n > 0 && width > 0 && bits > 0)
+        CGNN_REQUIRE(x != nullptr && planes != nullptr, "cluster: null input");
+    if (dtype == CGNN_F32)
+        return project_typed<float>((const float *)x, (const float *)planes, n, width, bits,
+                                    (float *)proj, codes, stream);
+    return project_typed<double>((const double *)x, (const double *)planes, n, width, bits,
+                                 (double *)proj, codes, stream);
+}
+
+template <typename T>
+__global__ void codes_from_proj_kernel(const T *proj, int64_t n, int bits, int32_t *codes) {
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n;
+         r += (int64_t)blockDim.x * gridDim.x) {
+        int32_t id = 0;
+        for (int h = 0; h < bits; ++h) id = (id << 1) | (proj[r * bits + h] > T(0) ? 1 : 0);
+        codes[r] = id;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// Compaction of raw codes.  Workspace layout (all int32 unless noted), n rows:
+//   keys[2][n]  vals[2][n]  cid[n]  segstart[n+2]  active[1]  pad  | cub temp (bytes)
+// After cgnn_cluster_assign: vals[0] = permutation (rows sorted by code, ascending row
+// inside a bucket), segstart[b] = first sorted position of bucket b (b = 1..active),
+// segstart[0] = 0 (bucket 0 is always empty), segstart[active+1] = n.
+// ---------------------------------------------------------------------------------------
+struct AssignLayout {
+    int32_t *keys[2];
+    int32_t *vals[2];
+    int32_t *cid;
+    int32_t *segstart;
+    int32_t *active;
+    void *temp;
+    size_t temp_bytes;
+    size_t total;
+};
+
+static size_t cub_temp_bytes(int64_t n) {
+    size_t sort_bytes = 0, scan_bytes = 0;
+    cub::DoubleBuffer<int32_t> k(nullptr, nullptr), v(nullptr, nullptr);
+    const int num = (int)std::max<int64_t>(n, 1);
+    cub::DeviceRadixSort::SortPairs(nullptr, sort_bytes, k, v, num, 0, 32);
+    cub::DeviceScan::InclusiveSum(nullptr, scan_bytes, (const int32_t *)nullptr, (int32_t *)nullptr, num);
+    cub::DeviceScan::ExclusiveSum(nullptr, scan_bytes, (const int32_t *)nullptr, (int32_t *)nullptr, num + 2);
+    return align_up(std::max(sort_bytes, scan_bytes) + 256, 256);
+}
+
+static AssignLayout assign_layout(void *base, int64_t n) {
+    AssignLayout L;
+    const size_t nn = align_up(sizeof(int32_t) * (size_t)std::max<int64_t>(n, 1), 256);
+    char *p = reinterpret_cast<char *>(base);
+    size_t off = 0;
+    for (int i = 0; i < 2; ++i) { L.keys[i] = reinterpret_cast<int32_t *>(p + off); off += nn; }
+    for (int i = 0; i < 2; ++i) { L.vals[i] = reinterpret_cast<int32_t *>(p + off); off += nn; }
+    L.cid = reinterpret_cast<int32_t *>(p + off); off += nn;
+    L.segstart = reinterpret_cast<int32_t *>(p + off); off += nn + 256;
+    L.active = reinterpret_cast<int32_t *>(p + off); off += 256;
+    L.temp = p + off;
+    L.temp_bytes = cub_temp_bytes(n);
+    L.total = off + L.temp_bytes;
+    return L;
+}
+
+__global__ void iota_kernel(int32_t *v, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)blockDim.x * gridDim.x)
+        v[i] = (int32_t)i;
+}
+
+__global__ void head_flags_kernel(const int32_t *sorted, int32_t *flags, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)blockDim.x * gridDim.x)
+        flags[i] = (i == 0 || sorted[i] != sorted[i - 1]) ? 1 : 0;
+}
+
+__global__ void scatter_ids_kernel(const int32_t *perm, const int32_t *cid, const int32_t *flags,
+                                   int64_t n, int64_t *ids, int32_t *segstart, int32_t *active) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)blockDim.x * gridDim.x) {
+        const int32_t c = cid[i];
+        ids[perm[i]] = c;
+        if (flags[i]) segstart[c] = (int32_t)i;
+        if (i == 0) segstart[0] = 0;
+        if (i == n - 1) {
+            segstart[c + 1] = (int32_t)n;
+            *active = c;
+        }
+    }
+}
+
+__global__ void counts_kernel(const int32_t *segstart, int64_t active, int32_t *counts) {
+    for (int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; b <= active;
+         b += (int64_t)blockDim.x * gridDim.x)
+        counts[b] = b == 0 ? 0 : segstart[b + 1] - segstart[b];
+}
+
+__global__ void index_to_key_kernel(const int64_t *index, int64_t n, int64_t groups, int32_t *keys,
+                                    int32_t *hist) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)blockDim.x * gridDim.x) {
+        const int64_t g = index[i];
+        if (g < 0 || g >= groups) {
+            atomicOr(&g_cluster_status, STATUS_BAD_INDEX);
+            keys[i] = 0;
+            atomicAdd(hist, 1);
+        } else {
+            keys[i] = (int32_t)g;
+            atomicAdd(hist + g, 1);  // integer atomics: order-independent result
+        }
+    }
+}
+
+static unsigned grid_for(int64_t n) { return (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(n, 256), 148 * 16)); }
+
+// Sort (key,row) pairs by the low `bits` bits of the key; leaves sorted keys in keys_out and
+// the permutation in vals[0].
+static int sort_pairs(AssignLayout &L, int64_t n, int bits, int32_t **sorted_keys,
+                      cudaStream_t stream) {
+    iota_kernel<<<grid_for(n), 256, 0, stream>>>(L.vals[0], n);
+    CGNN_LAUNCH_CHECK();
+    if (bits == 0) {
+        *sorted_keys = L.keys[0];
+        return CGNN_OK;
+    }
+    cub::DoubleBuffer<int32_t> k(L.keys[0], L.keys[1]), v(L.vals[0], L.vals[1]);
+    size_t bytes = L.temp_bytes;
+    CGNN_CUDA(cub::DeviceRadixSort::SortPairs(L.temp, bytes, k, v, (int)n, 0, bits, stream));
+    if (v.Current() != L.vals[0])
+        CGNN_CUDA(cudaMemcpyAsync(L.vals[0], v.Current(), sizeof(int32_t) * (size_t)n,
+                                  cudaMemcpyDeviceToDevice, stream));
+    *sorted_keys = k.Current();
+    return CGNN_OK;
+}
+
+}  // namespace cgnn
+
+using namespace cgnn;
+
+extern "C" {
+
+int cgnn_cluster_project(int dtype, const void *x, const void *planes, int64_t n, int64_t width,
+                         int bits, void *proj, cgnn_stream_t stream) {
+    CGNN_REQUIRE(proj != nullptr || n == 0 || bits == 0, "cluster_project: null output");
+    return project(dtype, x, planes, n, width, bits, proj, nullptr, (cudaStream_t)stream);
+}
+
+int cgnn_cluster_codes(int dtype, const void *x, const void *planes, int64_t n, int64_t width,
+                       int bits, int32_t *codes, cgnn_stream_t stream) {
+    CGNN_REQUIRE(codes != nullptr || n == 0, "cluster_codes: null output");
+    return project(dtype, x, planes, n, width, bits, nullptr, codes, (cudaStream_t)stream);
+}
+
+int cgnn_cluster_codes_from_projection(int dtype, const void *proj, int64_t n, int bits,
+                                       int32_t *codes, cgnn_stream_t stream) {
+    CGNN_REQUIRE(dtype == CGNN_F32 || dtype == CGNN_F64, "cluster: unknown dtype %d", dtype);
+    CGNN_REQUIRE(bits >= 0 && bits <= 30, "cluster: hash bits must be in [0,30]");
+    CGNN_REQUIRE(n >= 0 && n <= 0x7fffffffll, "cluster: node count exceeds int32 capacity");
+    if (n == 0) return CGNN_OK;
+    CGNN_REQUIRE(codes != nullptr && (proj != nullptr || bits == 0), "cluster: null pointer");
+    if (dtype == CGNN_F32)
+        codes_from_proj_kernel<float><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(
+            (const float *)proj, n, bits, codes);
+    else
+        codes_from_proj_kernel<double><<<grid_for(n), 256, 0, (cudaStream_t)stream>>>(
+            (const double *)proj, n, bits, codes);
+    CGNN_LAUNCH_CHECK();
+    return CGNN_OK;
+}
+
+size_t cgnn_cluster_workspace_bytes(int64_t n, int bits) {
+    (void)bits;
+    if (n < 0 || n > 0x7fffffffll) return 0;
+    return assign_layout(nullptr, n).total;
+}
+
+int cgnn_cluster_assign(const int32_t *codes, int64_t n, int bits, void *workspace,
+                        size_t workspace_bytes, int64_t *ids, int64_t *active_out,
+                        cgnn_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    CGNN_REQUIRE(bits >= 0 && bits <= 30, "cluster_assign: hash bits must be in [0,30]");
+    CGNN_REQUIRE(n >= 0 && n <= 0x7fffffffll, "cluster_assign: node count exceeds int32 capacity");
+    CGNN_REQUIRE(active_out != nullptr, "cluster_assign: null active_out");
+    *active_out = 0;
+    if (n == 0) return CGNN_OK;
+    CGNN_REQUIRE(codes != nullptr && ids != nullptr && workspace != nullptr,
+                 "cluster_assign: null pointer");
+    CGNN_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0,
+                 "cluster_assign: workspace must be 256-byte aligned");
+    AssignLayout L = assign_layout(workspace, n);
+    CGNN_REQUIRE(workspace_bytes >= L.total, "cluster_assign: workspace of %zu bytes needed, %zu given",
+                 L.total, workspace_bytes);
+    CGNN_CUDA(cudaMemcpyAsync(L.keys[0], codes, sizeof(int32_t) * (size_t)n,
+                              cudaMemcpyDeviceToDevice, stream));
+    int32_t *sorted = nullptr;
+    int rc = sort_pairs(L, n, bits, &sorted, stream);
+    if (rc != CGNN_OK) return rc;
+    int32_t *flags = sorted == L.keys[0] ? L.keys[1] : L.keys[0];
+    head_flags_kernel<<<grid_for(n), 256, 0, stream>>>(sorted, flags, n);
+    CGNN_LAUNCH_CHECK();
+    size_t bytes = L.temp_bytes;
+    CGNN_CUDA(cub::DeviceScan::InclusiveSum(L.temp, bytes, flags, L.cid, (int)n, stream));
+    scatter_ids_kernel<<<grid_for(n), 256, 0, stream>>>(L.vals[0], L.cid, flags, n, ids, L.segstart,
+                                                        L.active);
+    CGNN_LAUNCH_CHECK();
+    int32_t active = 0;
+    CGNN_CUDA(cudaMemcpyAsync(&active, L.active, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    CGNN_CUDA(cudaStreamSynchronize(stream));
+    *active_out = active;
+    return CGNN_OK;
+}
+
+int cgnn_cluster_assign_export(const void *workspace, int64_t n, int64_t active, int32_t *counts,
+                               cgnn_plan **plan_out, int split, cgnn_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (plan_out) *plan_out = nullptr;
+    CGNN_REQUIRE(n >= 0 && active >= 0 && active <= n, "assign_export: bad sizes");
+    CGNN_REQUIRE(counts != nullptr, "assign_export: null counts");
+    if (n == 0) {
+        CGNN_CUDA(cudaMemsetAsync(counts, 0, sizeof(int32_t), stream));
+        return CGNN_OK;
+    }
+    CGNN_REQUIRE(workspace != nullptr, "assign_export: null workspace");
+    AssignLayout L = assign_layout(const_cast<void *>(workspace), n);
+    counts_kernel<<<grid_for(active + 1), 256, 0, stream>>>(L.segstart, active, counts);
+    CGNN_LAUNCH_CHECK();
+    if (!plan_out) return CGNN_OK;
+    cgnn_plan *p = new cgnn_plan();
+    CGNN_CUDA(cudaGetDevice(&p->device));
+    p->rows = active + 1;
+    p->nterms = 1;
+    p->nnz[0] = n;
+    CGNN_CUDA(cudaMalloc(&p->rowptr[0], sizeof(int32_t) * (size_t)(active + 2)));
+    CGNN_CUDA(cudaMalloc(&p->col[0], sizeof(int32_t) * (size_t)n));
+    CGNN_CUDA(cudaMemcpyAsync(p->rowptr[0], L.segstart, sizeof(int32_t) * (size_t)(active + 2),
+                              cudaMemcpyDeviceToDevice, stream));
+    CGNN_CUDA(cudaMemcpyAsync(p->col[0], L.vals[0], sizeof(int32_t) * (size_t)n,
+                              cudaMemcpyDeviceToDevice, stream));
+    int rc = plan_analyze(p, split, stream);
+    if (rc != CGNN_OK) {
+        cgnn_plan_destroy(p);
+        return rc;
+    }
+    *plan_out = p;
+    return CGNN_OK;
+}
+
+int cgnn_plan_create_from_index(cgnn_plan **plan_out, const int64_t *index, int64_t n,
+                                int64_t groups, int split, cgnn_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    CGNN_REQUIRE(plan_out != nullptr, "plan_from_index: null output");
+    *plan_out = nullptr;
+    CGNN_REQUIRE(n >= 0 && n < 0x7fffffffll && groups >= 0 && groups < 0x7fffffffll,
+                 "plan_from_index: size out of 32-bit range");
+    CGNN_REQUIRE(index != nullptr || n == 0, "plan_from_index: null index");
+    CGNN_REQUIRE(groups > 0 || n == 0, "plan_from_index: entries but no groups");
+    cgnn_plan *p = new cgnn_plan();
+    CGNN_CUDA(cudaGetDevice(&p->device));
+    p->rows = groups;
+    p->nterms = 1;
+    p->nnz[0] = n;
+    CGNN_CUDA(cudaMalloc(&p->rowptr[0], sizeof(int32_t) * (size_t)(groups + 1)));
+    CGNN_CUDA(cudaMalloc(&p->col[0], sizeof(int32_t) * (size_t)std::max<int64_t>(n, 1)));
+    void *ws = nullptr;
+    int32_t *hist = nullptr;
+    int rc = CGNN_OK;
+    do {
+        AssignLayout L0 = assign_layout(nullptr, n);
+        if (cudaMalloc(&ws, L0.total) != cudaSuccess ||
+            cudaMalloc(&hist, sizeof(int32_t) * (size_t)(groups + 1)) != cudaSuccess) {
+            set_error("plan_from_index: device allocation failed");
+            rc = CGNN_ERR_CUDA;
+            break;
+        }
+        AssignLayout L = assign_layout(ws, n);
+        cudaMemsetAsync(hist, 0, sizeof(int32_t) * (size_t)(groups + 1), stream);
+        if (n > 0) {
+            index_to_key_kernel<<<grid_for(n), 256, 0, stream>>>(index, n, groups, L.keys[0], hist);
+            int bits = 1;
+            while (bits < 31 && ((int64_t)1 << bits) < groups) ++bits;
+            int32_t *sorted = nullptr;
+            rc = sort_pairs(L, n, bits, &sorted, stream);
+            if (rc != CGNN_OK) break;
+            cudaMemcpyAsync(p->col[0], L.vals[0], sizeof(int32_t) * (size_t)n,
+                            cudaMemcpyDeviceToDevice, stream);
+        }
+        size_t bytes = L.temp_bytes;
+        // The scan temp was sized for max(n,1)+2 items; a histogram longer than that gets
+        // its own temp.
+        void *temp = L.temp;
+        void *own_temp = nullptr;
+        size_t need = 0;
+        cub::DeviceScan::ExclusiveSum(nullptr, need, hist, p->rowptr[0], (int)(groups + 1));
+        if (need > bytes) {
+            if (cudaMalloc(&own_temp, need) != cudaSuccess) {
+                set_error("plan_from_index: device allocation failed");
+                rc = CGNN_ERR_CUDA;
+                break;
+            }
+            temp = own_temp;
+            bytes = need;
+        }
+        cudaError_t e = cub::DeviceScan::ExclusiveSum(temp, bytes, hist, p->rowptr[0],
+                                                      (int)(groups + 1), stream);
+        cudaStreamSynchronize(stream);
+        if (own_temp) cudaFree(own_temp);
+        if (e != cudaSuccess) {
+            set_error("plan_from_index: scan failed: %s", cudaGetErrorString(e));
+            rc = CGNN_ERR_CUDA;
+            break;
+        }
+        int status = 0;
+        rc = cluster_status(&status);
+        if (rc != CGNN_OK) break;
+        if (status & STATUS_BAD_INDEX) {
+            set_error("plan_from_index: index value outside [0, %lld)", (long long)groups);
+            rc = CGNN_ERR_INVALID;
+            break;
+        }
+        rc = plan_analyze(p, split, stream);
+    } while (0);
+    if (ws) cudaFree(ws);
+    if (hist) cudaFree(hist);
+    if (rc != CGNN_OK) {
+        cgnn_plan_destroy(p);
+        return rc;
+    }
+    *plan_out = p;
+    return CGNN_OK;
+}
+
+}  // extern "C"

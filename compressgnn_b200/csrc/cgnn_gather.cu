@@ -1,0 +1,159 @@
+// Row expansion: out[r,:] = f(table[index[r],:]) for every node r.
+//
+// Serves the fused reconstruction (gather + bias + ReLU) and the mean backward (gather /
+// bucket size).  The table of representatives is small and stays in L2; the kernel is a
+// streaming writer of n*width elements, so it uses 128-bit streaming stores and keeps
+// several rows per lane group in flight.  A bad index sets a status bit and yields zeros
+// (the reference traps the GPU instead).
+#include <algorithm>
+
+#include "cgnn_plan.h"
+
+namespace cgnn {
+
+static __device__ int g_gather_status = 0;
+
+int gather_status(int *out) {
+    int zero = 0;
+    CGNN_CUDA(cudaMemcpyFromSymbol(out, g_gather_status, sizeof(int)));
+    CGNN_CUDA(cudaMemcpyToSymbol(g_gather_status, &zero, sizeof(int)));
+    return CGNN_OK;
+}
+
+template <typename T>
+struct ExpandArgs {
+    const T *table;
+    const int64_t *index;
+    const T *bias;              // optional [width]
+    const int32_t *div_counts;  // optional [groups]: divide by max(count[g], 1)
+    int relu;
+    T *out;
+    int64_t n, width, groups;
+};
+
+// LPR lanes own one output row at a time and walk it in steps of LPR vectors; RPG rows per
+// group are loaded before any is stored.
+template <typename T, int VW, int LPR, int RPG>
+__global__ void __launch_bounds__(256) expand_kernel(const ExpandArgs<T> a) {
+    using V = Vec<T, VW>;
+    constexpr int GPW = 32 / LPR;
+    const int lane = threadIdx.x & 31;
+    const int gl = lane & (LPR - 1);
+    const int64_t group = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * GPW + lane / LPR;
+    const int64_t ngroups = (int64_t)gridDim.x * (blockDim.x >> 5) * GPW;
+    const int64_t vecs = a.width / VW;
+    for (int64_t r0 = group * RPG; r0 < a.n; r0 += ngroups * RPG) {
+        int64_t g[RPG];
+        T divisor[RPG];
+#pragma unroll
+        for (int i = 0; i < RPG; ++i) {
+            g[i] = -1;
+            divisor[i] = T(1);
+            if (r0 + i < a.n) {
+                const int64_t gi = a.index[r0 + i];
+                if (gi < 0 || gi >= a.groups) {
+                    if (gl == 0) atomicOr(&g_gather_status, STATUS_BAD_INDEX);
+                } else {
+                    g[i] = gi;
+                    if (a.div_counts) divisor[i] = (T)max(a.div_counts[gi], 1);
+                }
+            }
+        }
+        for (int64_t c = gl; c < vecs; c += LPR) {
+            V x[RPG];
+            V b = vec_zero<T, VW>();
+            if (a.bias) b = vec_load<T, VW>(a.bias + c * VW);
+#pragma unroll
+            for (int i = 0; i < RPG; ++i)
+                x[i] = g[i] >= 0 ? vec_load<T, VW>(a.table + g[i] * a.width + c * VW)
+                                 : vec_zero<T, VW>();
+#pragma unroll
+            for (int i = 0; i < RPG; ++i) {
+                if (r0 + i < a.n) {
+                    V y;
+#pragma unroll
+                    for (int k = 0; k < VW; ++k) {
+                        T v = x[i].v[k];
+                        if (a.bias) v += b.v[k];
+                        if (a.div_counts) v = v / divisor[i];
+                        y.v[k] = (a.relu && v < T(0)) ? T(0) : v;
+                    }
+                    vec_store_cs<T, VW>(a.out + (r0 + i) * a.width + c * VW, y);
+                }
+            }
+        }
+    }
+}
+
+static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename T, int VW, int LPR>
+static int launch_expand(const ExpandArgs<T> &a, cudaStream_t stream) {
+    constexpr int RPG = 4;
+    const int64_t groups_needed = ceil_div(a.n, RPG);
+    const int64_t per_block = 8 * (32 / LPR);
+    const int64_t blocks = std::min<int64_t>(ceil_div(groups_needed, per_block), 148 * 32);
+    expand_kernel<T, VW, LPR, RPG><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    CGNN_LAUNCH_CHECK();
+    return CGNN_OK;
+}
+
+template <typename T>
+static int expand_typed(const ExpandArgs<T> &a, cudaStream_t stream) {
+    constexpr int VWMAX = 16 / (int)sizeof(T);
+    if (a.n == 0 || a.width == 0) return CGNN_OK;
+    const bool vec = a.width % VWMAX == 0 && aligned16(a.table) && aligned16(a.out) &&
+                     aligned16(a.bias);
+    if (vec) {
+        const int64_t vecs = a.width / VWMAX;
+        if (vecs <= 4) return launch_expand<T, VWMAX, 4>(a, stream);
+        if (vecs <= 8) return launch_expand<T, VWMAX, 8>(a, stream);
+        if (vecs <= 16) return launch_expand<T, VWMAX, 16>(a, stream);
+        return launch_expand<T, VWMAX, 32>(a, stream);
+    }
+    if (a.width <= 4) return launch_expand<T, 1, 4>(a, stream);
+    if (a.width <= 8) return launch_expand<T, 1, 8>(a, stream);
+    if (a.width <= 16) return launch_expand<T, 1, 16>(a, stream);
+    return launch_expand<T, 1, 32>(a, stream);
+}
+
+static int expand(int dtype, int64_t n, int64_t width, int64_t groups, const void *table,
+                  const int64_t *index, const void *bias, const int32_t *div_counts, int relu,
+                  void *out, cudaStream_t stream) {
+    CGNN_REQUIRE(dtype == CGNN_F32 || dtype == CGNN_F64, "gather: unknown dtype %d", dtype);
+    CGNN_REQUIRE(n >= 0 && width >= 0 && groups >= 0, "gather: negative size");
+    if (n > 0 && width > 0)
+        CGNN_REQUIRE(table != nullptr && index != nullptr && out != nullptr,
+                     "gather: null pointer");
+    if (dtype == CGNN_F32) {
+        ExpandArgs<float> a{(const float *)table, index, (const float *)bias, div_counts, relu,
+                            (float *)out, n, width, groups};
+        return expand_typed<float>(a, stream);
+    }
+    ExpandArgs<double> a{(const double *)table, index, (const double *)bias, div_counts, relu,
+                         (double *)out, n, width, groups};
+    return expand_typed<double>(a, stream);
+}
+
+}  // namespace cgnn
+
+using namespace cgnn;
+
+extern "C" {
+
+int cgnn_cluster_mean_backward(int dtype, int64_t n, int64_t width, int64_t groups,
+                               const void *grad, const int64_t *index, const int32_t *count,
+                               void *out, cgnn_stream_t stream) {
+    CGNN_REQUIRE(count != nullptr || n == 0, "mean_backward: null counts");
+    return expand(dtype, n, width, groups, grad, index, nullptr, count, 0, out,
+                  (cudaStream_t)stream);
+}
+
+int cgnn_cluster_reconstruct(int dtype, int64_t n, int64_t width, int64_t groups,
+                             const void *reps, const int64_t *index, const void *bias, int relu,
+                             void *out, cgnn_stream_t stream) {
+    return expand(dtype, n, width, groups, reps, index, bias, nullptr, relu, out,
+                  (cudaStream_t)stream);
+}
+
+}  // extern "C"

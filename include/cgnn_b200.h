@@ -1,0 +1,170 @@
+/*
+ * cgnn_b200 -- C ABI of the B200 (sm_100a) kernels behind CompressGNN's runtime operators.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, returns an int
+ * status (0 = ok) and never throws, traps or blocks the device.  The message for the last
+ * non-zero status of the calling thread is returned by cgnn_last_error().  Paths cited as
+ * "ref:" are files of ZhengChenCS/CompressGNN whose operator the entry point replaces.
+ *
+ * dtype: CGNN_F32 or CGNN_F64 (the reference dispatches both, ref:
+ * src/runtime/csrc/sparse/cuda/spmm_gpu.cu:37).  All matrices are dense row-major with
+ * row stride == width.  Index arrays handed to plan constructors may be 4 or 8 bytes wide;
+ * plans keep private 32-bit copies.
+ */
+#ifndef CGNN_B200_H
+#define CGNN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st *cgnn_stream_t; /* a cudaStream_t */
+
+enum { CGNN_OK = 0, CGNN_ERR_INVALID = 1, CGNN_ERR_CUDA = 2, CGNN_ERR_CAPACITY = 3 };
+enum { CGNN_F32 = 0, CGNN_F64 = 1 };
+
+int cgnn_version(void);
+const char *cgnn_last_error(void);
+
+/* OR of the status bits recorded by kernels since the last call (1 = an index outside its
+ * range was met and skipped, 2 = a bounded wait ran out, 4 = malformed CSR); clears the
+ * word.  Synchronises the device.  The reference traps the GPU on a bad index instead
+ * (ref: src/runtime/csrc/cluster/cuda/cluster_kernel.cu:66,82,92,104). */
+int cgnn_device_status(int *status_out);
+
+/* ---------------------------------------------------------------------------------------
+ * Segment plans.  A plan describes "rows that sum gathered source rows": a CSR block (or
+ * two blocks over the same rows whose sums are fused), cut into work units by the row
+ * degree histogram: rows up to `split` entries are owned by one lane group; longer rows
+ * are cut into chunks of `split` entries whose partial sums are combined in chunk order
+ * by the last chunk to finish (deterministic; no floating-point atomics).
+ * ------------------------------------------------------------------------------------- */
+typedef struct cgnn_plan cgnn_plan;
+
+/* Build a plan from device CSR arrays (rowptr[rows+1], col[nnz]); term 1 may be absent
+ * (rowptr1 == NULL).  split == 0 picks the chunk length from the degree histogram.
+ * Allocates plan-owned device memory and synchronises `stream` (one-off, at graph load).
+ * Replaces the per-call kernel choice of ref: layer/CompressgnnSPMM.py:14-19. */
+int cgnn_plan_create(cgnn_plan **plan_out, int64_t rows, int index_bytes,
+                     const void *rowptr0, const void *col0, int64_t nnz0,
+                     const void *rowptr1, const void *col1, int64_t nnz1,
+                     int split, cgnn_stream_t stream);
+
+/* Build a plan that groups the positions of index[n] (values in [0, groups)) by value,
+ * positions ascending inside a group: the segments the mean / reconstruct-backward
+ * reductions run over.  Sorts on the device; synchronises `stream`. */
+int cgnn_plan_create_from_index(cgnn_plan **plan_out, const int64_t *index, int64_t n,
+                                int64_t groups, int split, cgnn_stream_t stream);
+
+void cgnn_plan_destroy(cgnn_plan *plan);
+
+/* info[0..7] = rows, nnz (both terms), split, long rows, chunks, direct work units,
+ * terms, 1 if a compact row list is used. */
+int cgnn_plan_info(const cgnn_plan *plan, int64_t info[8]);
+
+/* Bytes of caller-provided scratch a launch over `width` columns needs.  The first
+ * cgnn_plan_ticket_bytes() bytes hold chunk tickets: they must be zero before the first
+ * launch and are left zero by every launch, so one zero-initialised buffer can serve any
+ * number of plans as long as their launches do not overlap on the device. */
+size_t cgnn_plan_scratch_bytes(const cgnn_plan *plan, int64_t width, int dtype);
+size_t cgnn_plan_ticket_bytes(const cgnn_plan *plan, int64_t width, int dtype);
+
+/* ---------------------------------------------------------------------------------------
+ * SpMM:  out[r,:] (+)= sum_e val[e] * src[col[e],:]
+ * ref: spmm_func, src/runtime/csrc/sparse/spmm.cpp:11-23 and
+ *      src/runtime/csrc/sparse/cuda/spmm_gpu.cu:8-107 (all six kernel variants).
+ * val may be NULL (all ones).  accumulate != 0 adds to the existing out (the reference's
+ * optional_out contract); out may alias src when the rows written are never read (the
+ * in-place rule-level updates of ref: layer/CompressgnnSPMM.py:57-58).
+ * ------------------------------------------------------------------------------------- */
+int cgnn_spmm(const cgnn_plan *plan, int dtype, int64_t width, const void *val,
+              const void *src, void *out, int accumulate, void *scratch,
+              size_t scratch_bytes, cgnn_stream_t stream);
+
+/* Two blocks over the same output rows in one pass:
+ *   out[r,:] (+)= sum_e val0[e]*src0[col0[e],:] + sum_e val1[e]*src1[col1[e],:]
+ * (the plan must have been built with two terms).  Fuses the last two calls of the
+ * reference's forward (v2r then v2v, ref: layer/CompressgnnSPMM.py:59-60) and of its
+ * backward (:84-85) so that out is written once. */
+int cgnn_spmm_pair(const cgnn_plan *plan, int dtype, int64_t width, const void *val0,
+                   const void *src0, const void *val1, const void *src1, void *out,
+                   int accumulate, void *scratch, size_t scratch_bytes, cgnn_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * LSH cluster assignment.
+ * ref: cluster_assign_cuda, src/runtime/csrc/cluster/cuda/cluster_kernel.cu:118-153;
+ *      CPU LSH, src/runtime/csrc/cluster/cpu/cluster_cpu.cpp:27-70.
+ * ------------------------------------------------------------------------------------- */
+
+/* proj[n,bits] = x[n,width] . planes[width,bits], each entry accumulated as
+ * p = fma(x[r,k], planes[k,h], p) for k ascending from p = +0 (the documented order the
+ * CPU oracle restates).  Used alone by the column-sharded path, whose partial
+ * projections are summed across GPUs before sign packing. */
+int cgnn_cluster_project(int dtype, const void *x, const void *planes, int64_t n,
+                         int64_t width, int bits, void *proj, cgnn_stream_t stream);
+
+/* codes[r] = sign bits of proj[r,:], MSB first, bit = (p > 0)  (ref: hash_ids,
+ * cluster_kernel.cu:41-50). */
+int cgnn_cluster_codes_from_projection(int dtype, const void *proj, int64_t n, int bits,
+                                       int32_t *codes, cgnn_stream_t stream);
+
+/* Fused projection + sign packing; the n x bits projection never reaches memory. */
+int cgnn_cluster_codes(int dtype, const void *x, const void *planes, int64_t n,
+                       int64_t width, int bits, int32_t *codes, cgnn_stream_t stream);
+
+/* Bytes of workspace cgnn_cluster_assign needs for n rows. */
+size_t cgnn_cluster_workspace_bytes(int64_t n, int bits);
+
+/* Compact the raw codes: ids[r] in 1..active ascend with the raw code; returns `active`
+ * through *active_out after one stream synchronisation (the reference's single .item(),
+ * cluster_kernel.cu:147).  The workspace afterwards holds the per-bucket counts and the
+ * bucket permutation; read them with cgnn_cluster_assign_export. */
+int cgnn_cluster_assign(const int32_t *codes, int64_t n, int bits, void *workspace,
+                        size_t workspace_bytes, int64_t *ids, int64_t *active_out,
+                        cgnn_stream_t stream);
+
+/* counts[active+1] (counts[0] == 0, ref: tests/test_transformation.py:39) and a plan
+ * over the buckets (rows = active+1) built from the permutation already in the workspace. */
+int cgnn_cluster_assign_export(const void *workspace, int64_t n, int64_t active,
+                               int32_t *counts, cgnn_plan **plan_out, int split,
+                               cgnn_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Mean representatives and reconstruction.
+ * ------------------------------------------------------------------------------------- */
+
+/* out[g,:] = sum_{index[r]==g} x[r,:] / max(count[g],1); plan from
+ * cgnn_cluster_assign_export or cgnn_plan_create_from_index.
+ * ref: cluster_mean_cuda, cluster_kernel.cu:158-170 (float atomics there). */
+int cgnn_cluster_mean(const cgnn_plan *plan, int dtype, int64_t width, const void *x,
+                      const int32_t *count, void *out, void *scratch, size_t scratch_bytes,
+                      cgnn_stream_t stream);
+
+/* out[r,:] = grad[index[r],:] / max(count[index[r]],1)
+ * ref: cluster_mean_backward_cuda, cluster_kernel.cu:171-181. */
+int cgnn_cluster_mean_backward(int dtype, int64_t n, int64_t width, int64_t groups,
+                               const void *grad, const int64_t *index, const int32_t *count,
+                               void *out, cgnn_stream_t stream);
+
+/* out[r,:] = act(reps[index[r],:] + bias[:]); bias may be NULL; relu: v < 0 ? 0 : v.
+ * ref: cluster_reconstruct_cuda, cluster_kernel.cu:182-195. */
+int cgnn_cluster_reconstruct(int dtype, int64_t n, int64_t width, int64_t groups,
+                             const void *reps, const int64_t *index, const void *bias,
+                             int relu, void *out, cgnn_stream_t stream);
+
+/* d_reps[g,:] = sum_{index[r]==g} (relu && output[r,:] <= 0 ? 0 : grad[r,:]);
+ * bias_grad (optional, [width]) = column sums of d_reps, the value the reference derives
+ * in Python (ref: layer/CompressgnnReconstruct.py:26).
+ * ref: cluster_reconstruct_backward_cuda, cluster_kernel.cu:196-208 (float atomics there). */
+int cgnn_cluster_reconstruct_backward(const cgnn_plan *plan, int dtype, int64_t width,
+                                      const void *grad, const void *output, int relu,
+                                      void *d_reps, void *bias_grad, void *scratch,
+                                      size_t scratch_bytes, cgnn_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CGNN_B200_H */

@@ -1,0 +1,101 @@
+"""Build the reference's own CPU code into ``oracle/_ref/`` (test infrastructure only).
+
+Nothing here is product code.  The script compiles, with plain ``g++`` command lines and
+*from the sources where they lie* in a checkout of ZhengChenCS/CompressGNN, two Python
+extension modules:
+
+``compressgnn_runtime``  (reference ``src/runtime/csrc``: ``function.cpp``,
+    ``sparse/spmm.cpp``, ``sparse/cpu/spmm_cpu.cpp``, ``cluster/cluster.cpp``,
+    ``cluster/cpu/cluster_cpu.cpp``) -- the CPU operators ``spmm_func`` and
+    ``cluster_forward`` that the parity tests and the bench's CPU baseline call.
+
+``compressgnn_offline``  (reference ``src/offline/csrc/function.cpp`` + ``Gorder/*.cpp``)
+    -- graph preparation helpers (``filter_csr``, ``depth_filter_csr``,
+    ``hybird_partition``, ``topo_partition``, norms, ...).  The reference's grammar
+    compressor lives in an un-vendored git submodule, so ``bind_batch_cpu`` is satisfied
+    by the no-op stub ``ref_offline_stub.cpp`` next to this file.  ``-DNDEBUG`` is needed
+    because ``gen_mask.h:240`` carries an assert that can never hold.
+
+The outputs are git-ignored shared objects; no reference source is copied.  When the
+reference checkout is absent (the GPU box) the script does nothing and the prebuilt files
+that travelled with the tree are used.
+"""
+import os
+import subprocess
+import sys
+import sysconfig
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+OUT = HERE / "_ref"
+DEFAULT_REFERENCE = Path(os.environ.get("CGNN_REFERENCE_DIR", "/root/reference"))
+
+
+def _run(cmd):
+    print("[oracle/_ref]", " ".join(str(c) for c in cmd), flush=True)
+    subprocess.run([str(c) for c in cmd], check=True)
+
+
+def _newer(target, sources):
+    if not target.is_file():
+        return False
+    t = target.stat().st_mtime
+    return all(Path(s).stat().st_mtime <= t for s in sources)
+
+
+def build_runtime(ref):
+    import torch
+    from torch.utils import cpp_extension
+
+    csrc = ref / "src" / "runtime" / "csrc"
+    sources = [csrc / "function.cpp", csrc / "sparse" / "spmm.cpp",
+               csrc / "sparse" / "cpu" / "spmm_cpu.cpp", csrc / "cluster" / "cluster.cpp",
+               csrc / "cluster" / "cpu" / "cluster_cpu.cpp"]
+    target = OUT / "compressgnn_runtime.so"
+    if _newer(target, sources):
+        return target
+    torch_lib = Path(torch.__file__).parent / "lib"
+    cmd = ["g++", "-O3", "-fopenmp", "-std=c++17", "-shared", "-fPIC",
+           "-DTORCH_EXTENSION_NAME=compressgnn_runtime", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-I", csrc, "-I", sysconfig.get_paths()["include"]]
+    for inc in cpp_extension.include_paths():
+        cmd += ["-isystem", inc]
+    cmd += sources
+    cmd += ["-L", torch_lib, f"-Wl,-rpath,{torch_lib}", "-lc10", "-ltorch", "-ltorch_cpu",
+            "-ltorch_python", "-o", target]
+    _run(cmd)
+    return target
+
+
+def build_offline(ref):
+    import pybind11
+
+    csrc = ref / "src" / "offline" / "csrc"
+    sources = [csrc / "function.cpp"] + sorted((csrc / "Gorder").glob("*.cpp"))
+    sources.append(HERE / "ref_offline_stub.cpp")
+    target = OUT / "compressgnn_offline.so"
+    if _newer(target, sources):
+        return target
+    cmd = ["g++", "-O3", "-DNDEBUG", "-std=c++17", "-fopenmp", "-shared", "-fPIC", "-w",
+           "-I", csrc, "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"]]
+    cmd += sources + ["-o", target]
+    _run(cmd)
+    return target
+
+
+def build(reference_dir=DEFAULT_REFERENCE, quiet=False):
+    """Compile both modules when the reference checkout exists; return what is usable."""
+    ref = Path(reference_dir)
+    OUT.mkdir(exist_ok=True)
+    if (ref / "src" / "runtime" / "csrc" / "function.cpp").is_file():
+        build_runtime(ref)
+        build_offline(ref)
+    elif not quiet:
+        print("[oracle/_ref] reference checkout not found; using prebuilt files if present")
+    return {name: (OUT / f"{name}.so").is_file()
+            for name in ("compressgnn_runtime", "compressgnn_offline")}
+
+
+if __name__ == "__main__":
+    print(build(Path(sys.argv[1]) if len(sys.argv) > 1 else DEFAULT_REFERENCE))

@@ -1,0 +1,238 @@
+"""TEST INFRASTRUCTURE -- numpy front end of the CPU oracle (``cgnn_oracle.c``).
+
+Only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline legs import
+this module; the product package never does.  The arithmetic lives in ``cgnn_oracle.c``
+(each function cites the reference lines it follows); this file compiles it with gcc,
+wraps it for numpy arrays, and composes the level-ordered compressed propagation exactly
+in the call order of the reference's ``layer/CompressgnnSPMM.py``.
+
+Parity pin: ``tests/test_oracle_pins.py`` checks every function here against the
+reference's own CPU operators (``oracle/_ref``, built by ``build_ref.py`` from the
+reference sources) and against the committed fixtures in ``tests/golden/``.
+"""
+import ctypes
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+_SRC = HERE / "cgnn_oracle.c"
+_LIB = HERE / "libcgnn_oracle.so"
+_lib = None
+
+
+def build(force=False):
+    """Compile the C restatement next to its source (gcc only, no other dependency)."""
+    if force or not _LIB.is_file() or _LIB.stat().st_mtime < _SRC.stat().st_mtime:
+        subprocess.run(["gcc", "-O2", "-ffp-contract=off", "-shared", "-fPIC", str(_SRC),
+                        "-lm", "-o", str(_LIB)], check=True)
+    return _LIB
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(str(build()))
+    return _lib
+
+
+def _p(a):
+    return a.ctypes.data_as(ctypes.c_void_p) if a is not None else None
+
+
+def _suf(dtype):
+    dtype = np.dtype(dtype)
+    if dtype == np.float32:
+        return "f32"
+    if dtype == np.float64:
+        return "f64"
+    raise TypeError("oracle supports float32/float64 only")
+
+
+def _c(a, dtype):
+    return np.ascontiguousarray(a, dtype=dtype)
+
+
+def _check(rc, what):
+    if rc:
+        raise RuntimeError(f"oracle {what} failed with status {rc}")
+
+
+# ---------------------------------------------------------------------------------------
+# SpMM and compressed propagation
+# ---------------------------------------------------------------------------------------
+def spmm(rowptr, col, val, mat, out=None):
+    """``spmm_func(vlist, elist, value, mat, "rowbalance", out)`` on the CPU.
+
+    Accumulates into ``out`` in place when given (and returns it), else into zeros.
+    """
+    mat = np.ascontiguousarray(mat)
+    suf = _suf(mat.dtype)
+    rowptr, col = _c(rowptr, np.int64), _c(col, np.int64)
+    val = _c(val, mat.dtype)
+    rows, width = rowptr.size - 1, mat.shape[1]
+    if out is None:
+        out = np.zeros((rows, width), dtype=mat.dtype)
+    assert out.flags.c_contiguous and out.shape == (rows, width) and out.dtype == mat.dtype
+    fn = getattr(lib(), f"oracle_spmm_rowbalance_{suf}")
+    _check(fn(_p(rowptr), _p(col), _p(val), _p(mat), ctypes.c_int64(rows),
+              ctypes.c_int64(width), _p(out)), "spmm")
+    return out
+
+
+def transpose_csr(rowptr, col, val, ncols):
+    """Stable CSR transpose (entries of a column keep ascending row order), the data
+    movement ``torch_sparse.SparseTensor.csc()`` performs for the reference
+    (layer/CompressgnnSPMM.py:68-70, loader/CompressgnnData.py:180)."""
+    rowptr, col = _c(rowptr, np.int64), _c(col, np.int64)
+    rows = np.repeat(np.arange(rowptr.size - 1, dtype=np.int64), np.diff(rowptr))
+    order = np.argsort(col, kind="stable")
+    tptr = np.zeros(ncols + 1, dtype=np.int64)
+    np.cumsum(np.bincount(col, minlength=ncols), out=tptr[1:])
+    return tptr, rows[order], np.asarray(val)[order]
+
+
+def propagate_forward(blocks, x):
+    """Forward of ``Compressgnn_SPMM_Function`` (layer/CompressgnnSPMM.py:47-53):
+    r2v, the r2r levels in place, v2r, then v2v accumulated.  ``blocks`` maps
+    ``"v2v" | "v2r" | "r2v"`` to ``(rowptr, col, val)`` and ``"r2r"`` to a list of them."""
+    rule_out = spmm(*blocks["r2v"], x)
+    for level in blocks["r2r"]:
+        rule_out = spmm(*level, rule_out, out=rule_out)
+    out = spmm(*blocks["v2r"], rule_out)
+    return spmm(*blocks["v2v"], x, out=out)
+
+
+def propagate_backward(blocks, grad, n, r):
+    """Backward in the order of the reference's GPU branch
+    (layer/CompressgnnSPMM.py:65-70,80-85): transposed blocks, levels reversed.  (The
+    reference's CPU branch at :71-78 cannot run: empty range, undefined names.)"""
+    v2v_t = transpose_csr(*blocks["v2v"], n)
+    v2r_t = transpose_csr(*blocks["v2r"], r)   # [r, n]
+    r2v_t = transpose_csr(*blocks["r2v"], n)   # [n, r]
+    rule_out = spmm(*v2r_t, grad)
+    for level in reversed(blocks["r2r"]):
+        rule_out = spmm(*transpose_csr(*level, r), rule_out, out=rule_out)
+    out = spmm(*v2v_t, grad)
+    return spmm(*r2v_t, rule_out, out=out)
+
+
+# ---------------------------------------------------------------------------------------
+# Cluster / reconstruct
+# ---------------------------------------------------------------------------------------
+def project(x, planes, shards=1):
+    x, planes = np.ascontiguousarray(x), np.ascontiguousarray(planes)
+    suf = _suf(x.dtype)
+    n, width = x.shape
+    bits = planes.shape[1]
+    proj = np.zeros((n, bits), dtype=x.dtype)
+    if shards == 1:
+        fn = getattr(lib(), f"oracle_project_{suf}")
+        _check(fn(_p(x), _p(planes), ctypes.c_int64(n), ctypes.c_int64(width), bits, _p(proj)),
+               "project")
+    else:
+        assert suf == "f32"
+        _check(lib().oracle_project_sharded_f32(_p(x), _p(planes), ctypes.c_int64(n),
+                                                ctypes.c_int64(width), bits, int(shards),
+                                                _p(proj)), "project_sharded")
+    return proj
+
+
+def codes_from_projection(proj):
+    proj = np.ascontiguousarray(proj)
+    n, bits = proj.shape
+    codes = np.zeros(n, dtype=np.int32)
+    fn = getattr(lib(), f"oracle_codes_{_suf(proj.dtype)}")
+    _check(fn(_p(proj), ctypes.c_int64(n), bits, _p(codes)), "codes")
+    return codes
+
+
+def assign_from_codes(codes, bits):
+    codes = _c(codes, np.int32)
+    n = codes.size
+    ids = np.zeros(n, dtype=np.int64)
+    counts = np.zeros(n + 1, dtype=np.int32)
+    active = ctypes.c_int64(0)
+    _check(lib().oracle_assign(_p(codes), ctypes.c_int64(n), int(bits), _p(ids), _p(counts),
+                               ctypes.byref(active)), "assign")
+    return ids, counts[:active.value + 1].copy(), int(active.value)
+
+
+def cluster_assign(x, planes, shards=1):
+    """``(ids int64[N] 1-based, counts int32[active+1], active)`` as
+    ``layer/CompressgnnCluster.py:41-50`` returns them."""
+    proj = project(x, planes, shards)
+    return assign_from_codes(codes_from_projection(proj), planes.shape[1])
+
+
+def _cluster_call(name, dtype, *args):
+    fn = getattr(lib(), f"oracle_{name}_{_suf(dtype)}")
+    _check(fn(*args), name)
+
+
+def cluster_mean(x, index, counts):
+    x = np.ascontiguousarray(x)
+    index, counts = _c(index, np.int64), _c(counts, np.int32)
+    out = np.zeros((counts.size, x.shape[1]), dtype=x.dtype)
+    _cluster_call("mean", x.dtype, _p(x), _p(index), _p(counts), ctypes.c_int64(x.shape[0]),
+                  ctypes.c_int64(x.shape[1]), ctypes.c_int64(counts.size), _p(out))
+    return out
+
+
+def cluster_mean_backward(grad, index, counts):
+    grad = np.ascontiguousarray(grad)
+    index, counts = _c(index, np.int64), _c(counts, np.int32)
+    out = np.zeros((index.size, grad.shape[1]), dtype=grad.dtype)
+    _cluster_call("mean_backward", grad.dtype, _p(grad), _p(index), _p(counts),
+                  ctypes.c_int64(index.size), ctypes.c_int64(grad.shape[1]),
+                  ctypes.c_int64(counts.size), _p(out))
+    return out
+
+
+def reconstruct(reps, index, bias=None, relu=False):
+    reps = np.ascontiguousarray(reps)
+    index = _c(index, np.int64)
+    bias = None if bias is None else _c(bias, reps.dtype)
+    out = np.zeros((index.size, reps.shape[1]), dtype=reps.dtype)
+    _cluster_call("reconstruct", reps.dtype, _p(reps), _p(index), _p(bias), int(bool(relu)),
+                  ctypes.c_int64(index.size), ctypes.c_int64(reps.shape[1]),
+                  ctypes.c_int64(reps.shape[0]), _p(out))
+    return out
+
+
+def reconstruct_backward(grad, index, output, groups, relu=False):
+    """Returns ``(d_reps [groups, F], d_bias [F])``."""
+    grad, output = np.ascontiguousarray(grad), np.ascontiguousarray(output)
+    index = _c(index, np.int64)
+    out = np.zeros((groups, grad.shape[1]), dtype=grad.dtype)
+    bias_grad = np.zeros(grad.shape[1], dtype=grad.dtype)
+    _cluster_call("reconstruct_backward", grad.dtype, _p(grad), _p(output), _p(index),
+                  int(bool(relu)), ctypes.c_int64(index.size), ctypes.c_int64(grad.shape[1]),
+                  ctypes.c_int64(groups), _p(out), _p(bias_grad))
+    return out, bias_grad
+
+
+# ---------------------------------------------------------------------------------------
+# The compiled reference (oracle/_ref), when present
+# ---------------------------------------------------------------------------------------
+def reference_modules():
+    """Import ``compressgnn_runtime`` / ``compressgnn_offline`` built from the reference's
+    own sources by ``build_ref.py``.  Returns ``(runtime, offline)``; either is ``None``
+    when its shared object is absent."""
+    ref_dir = HERE / "_ref"
+    mods = []
+    if str(ref_dir) not in sys.path:
+        sys.path.insert(0, str(ref_dir))
+    for name in ("compressgnn_runtime", "compressgnn_offline"):
+        mod = None
+        if (ref_dir / f"{name}.so").is_file():
+            try:
+                if name == "compressgnn_runtime":
+                    import torch  # noqa: F401  (libtorch symbols must be loaded first)
+                mod = __import__(name)
+            except ImportError:
+                mod = None
+        mods.append(mod)
+    return tuple(mods)
