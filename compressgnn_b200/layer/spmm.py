@@ -1,0 +1,65 @@
+"""Compressed propagation: ``out = A_hat^T x`` evaluated through the rule DAG.
+
+Drop-in for the reference's ``layer/CompressgnnSPMM.py``: ``compress_spmm(graph, x)``,
+``Compressgnn_SPMM_Function`` (autograd, returns ``(None, grad_x)``) and the
+``Compressgnn_SPMM`` module.  Forward order (ref :54-60): rules gather the vertices that
+reference them (r2v), rule levels are folded in place parents-first (r2r), vertices gather
+their rules and their residual direct edges (v2r + v2v).  Backward (ref :80-85) runs the
+transposed blocks with the levels reversed.  Here the last two blocks of each direction are
+one fused launch, index arrays are 32-bit plan copies, and nothing is done on the CPU.
+"""
+import torch
+from torch import Tensor
+
+from ..loader.compress_graph import CompressGraph
+from .. import runtime as _native
+
+
+def _require_cuda(x):
+    if not x.is_cuda:
+        raise RuntimeError("compressgnn_b200 runs on CUDA tensors only (no CPU propagation path)")
+
+
+def _forward(graph, x):
+    _require_cuda(x)
+    x = x.contiguous()
+    plan = graph.propagation_plan()
+    dt = x.dtype
+    rule_out = _native.spmm_with_plan(plan.r2v, graph.r2v_graph.value_as(dt), x)
+    for level_plan, level in zip(plan.levels, graph.r2r_graph):
+        _native.spmm_with_plan(level_plan, level.value_as(dt), rule_out, out=rule_out, accumulate=True)
+    return _native.spmm_pair_with_plan(plan.out, graph.v2r_graph.value_as(dt), rule_out,
+                                       graph.v2v_graph.value_as(dt), x)
+
+
+def _backward(graph, grad):
+    _require_cuda(grad)
+    grad = grad.contiguous()
+    plan = graph.propagation_plan()
+    dt = grad.dtype
+    rule_out = _native.spmm_with_plan(plan.v2r_t, graph.v2r_graph.value_as(dt, True), grad)
+    for level_plan, level in zip(reversed(plan.levels_t), reversed(graph.r2r_graph)):
+        _native.spmm_with_plan(level_plan, level.value_as(dt, True), rule_out, out=rule_out, accumulate=True)
+    return _native.spmm_pair_with_plan(plan.out_t, graph.v2v_graph.value_as(dt, True), grad,
+                                       graph.r2v_graph.value_as(dt, True), rule_out)
+
+
+def compress_spmm(graph, x_j):
+    """Forward only, no autograd bookkeeping (ref: compress_spmm, :21-39)."""
+    return _forward(graph, x_j)
+
+
+class Compressgnn_SPMM_Function(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, graph, x_j):
+        ctx.graph = graph
+        return _forward(graph, x_j)
+
+    @staticmethod
+    def backward(ctx, grad_output: Tensor):
+        return None, _backward(ctx.graph, grad_output)
+
+
+class Compressgnn_SPMM(torch.nn.Module):
+    def forward(self, edge_index: CompressGraph, x_j: Tensor) -> Tensor:
+        return Compressgnn_SPMM_Function.apply(edge_index, x_j)

@@ -1,0 +1,70 @@
+"""The caller of the hot path: ``GNNLayer`` (propagate, then either a Linear on all nodes or
+cluster -> Linear on representatives -> fused reconstruct) and a GCN stack of them
+(ref: ``model/compressgnn/gcn.py:12-71``; the reference hard-wires three layers, here the
+depth is a parameter so the two-layer benchmark configurations can be built)."""
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+from .layer import Compressgnn_Cluster, Compressgnn_Reconstruct, KPropagate
+
+
+class GNNLayer(torch.nn.Module):
+    def __init__(self, in_features, out_features, param_H=1, use_transformation=False, refresh_interval=1,
+                 process_group=None):
+        super().__init__()
+        self.lin = torch.nn.Linear(in_features=in_features, out_features=out_features, bias=True)
+        self.P = KPropagate()
+        self.use_transformation = use_transformation
+        self.cluster = Compressgnn_Cluster(in_feature=in_features, param_H=param_H, training=True, cache=True,
+                                           index_cache=False, refresh_interval=refresh_interval,
+                                           process_group=process_group)
+        self.reconstruct = Compressgnn_Reconstruct()
+
+    def set_epoch(self, epoch, loss=None):
+        self.cluster.set_epoch(epoch, loss=loss)
+
+    def reset_cache(self):
+        self.cluster.reset_cache()
+
+    def forward(self, x: Tensor, edge_index, edge_weight=None, vertex_cnt: int = 0, rule_cnt: int = 0) -> Tensor:
+        x = self.P(x=x, edge_index=edge_index, edge_weight=edge_weight, vertex_cnt=vertex_cnt, rule_cnt=rule_cnt)
+        if self.use_transformation:
+            reps, index = self.cluster(x)
+            return self.reconstruct(F.linear(reps, self.lin.weight, None), index, bias=self.lin.bias)
+        return self.lin(x)
+
+
+class GCN(torch.nn.Module):
+    def __init__(self, in_features, out_features, hidden_features=128, param_H=1, dropout=0.3,
+                 use_transformation=False, refresh_interval=1, num_layers=3):
+        super().__init__()
+        dims = [in_features] + [hidden_features] * (num_layers - 1) + [out_features]
+        self.layers = torch.nn.ModuleList(
+            GNNLayer(dims[i], dims[i + 1], param_H=param_H, use_transformation=use_transformation,
+                     refresh_interval=refresh_interval) for i in range(num_layers))
+        self.dropout = dropout
+
+    def set_epoch(self, epoch, loss=None):
+        for layer in self.layers:
+            layer.set_epoch(epoch, loss=loss)
+
+    def reset_cache(self):
+        for layer in self.layers:
+            layer.reset_cache()
+
+    def _stack(self, x, edge_index, edge_weight, vertex_cnt, rule_cnt, dropout):
+        last = len(self.layers) - 1
+        for i, layer in enumerate(self.layers):
+            x = layer(x=x, edge_index=edge_index, edge_weight=edge_weight, vertex_cnt=vertex_cnt, rule_cnt=rule_cnt)
+            if i != last:
+                x = x.relu()
+                if dropout:
+                    x = F.dropout(x, p=self.dropout, training=self.training)
+        return F.log_softmax(x, dim=1)
+
+    def forward(self, x: Tensor, edge_index, edge_weight=None, vertex_cnt: int = 0, rule_cnt: int = 0) -> Tensor:
+        return self._stack(x, edge_index, edge_weight, vertex_cnt, rule_cnt, True)
+
+    def inference(self, x: Tensor, edge_index, edge_weight=None, vertex_cnt: int = 0, rule_cnt: int = 0) -> Tensor:
+        return self._stack(x, edge_index, edge_weight, vertex_cnt, rule_cnt, False)

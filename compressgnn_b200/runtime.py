@@ -22,7 +22,7 @@ from collections import OrderedDict
 
 import torch
 
-from ._lib import check, lib
+from ._lib import check, lib  # noqa: F401  (lib is re-exported for the layer modules)
 
 _METHODS = ("rowbalance_parreduce", "rowbalance_seqreduce", "rowbalance_rowcache",
             "nnzbalance_parreduce", "nnzbalance_seqreduce", "nnzbalance_rowcache")
@@ -397,6 +397,7 @@ def cluster_mean(input, index, count, plan=None):
         return out.zero_()
     if plan is None:
         plan = index_plan(index, groups)
+    _require(plan.rows == groups and plan.nnz == index.numel(), "cluster_mean: plan does not match index/count")
     code = _dtype_code(input)
     sp, sb = plan.scratch(width, code)
     with torch.cuda.device(input.device):
@@ -460,6 +461,8 @@ def cluster_reconstruct_backward(grad, index, output, groups, relu, plan=None,
         return (out, bias_grad.zero_()) if return_bias_grad else out
     if plan is None:
         plan = index_plan(index, groups)
+    _require(plan.rows == groups and plan.nnz == index.numel(),
+             "cluster_reconstruct_backward: plan does not match index/groups")
     code = _dtype_code(grad)
     sp, sb = plan.scratch(width, code)
     with torch.cuda.device(grad.device):

@@ -21,19 +21,24 @@ def golden():
 
 
 def assert_close_rel(actual, expected, rel=1e-5, what=""):
-    """|a - b| <= rel * max(|b|, rms(b)) element-wise.
+    """|a - b| <= rel * max(|b|, rms(row of b), rms(b)) element-wise.
 
     The stated floating-point bar of the hot path is rel 1e-5 in fp32.  A purely
     element-wise relative bound cannot hold for sums that cancel to ~0 under any change of
-    summation order, so small entries are measured against the RMS of the expected tensor.
+    summation order (the CPU reference itself is that far from the exact sum), so small
+    entries are measured against the RMS of their own output row -- rows are sums of very
+    different lengths on power-law graphs -- and of the whole tensor.
+    ``test_accuracy_against_fp64`` backs this with an fp64 computation.
     """
     a = np.asarray(actual, dtype=np.float64)
     b = np.asarray(expected, dtype=np.float64)
     assert a.shape == b.shape, f"{what}: shape {a.shape} != {b.shape}"
     if b.size == 0:
         return
-    rms = float(np.sqrt(np.mean(b * b)))
-    bound = rel * np.maximum(np.abs(b), rms) + 1e-30
+    scale = np.maximum(np.abs(b), float(np.sqrt(np.mean(b * b))))
+    if b.ndim == 2:
+        scale = np.maximum(scale, np.sqrt(np.mean(b * b, axis=1, keepdims=True)))
+    bound = rel * scale + 1e-30
     err = np.abs(a - b)
     worst = int(np.argmax(err - bound))
     assert np.all(err <= bound), (

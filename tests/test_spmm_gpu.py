@@ -60,6 +60,23 @@ def test_spmm_widths(rt, dtype, width):
     assert_close_rel(got.cpu().numpy(), ref_acc, what=f"spmm accumulate width {width}")
 
 
+def test_accuracy_against_fp64(rt):
+    """The fp32 CUDA result is as close to the exact (fp64) product as the reference's own
+    fp32 loop is: error no larger than twice the CPU oracle's, row by row in max norm."""
+    rng = np.random.default_rng(12)
+    rowptr, col = random_csr(rng, 400, 300, 30, long_rows=[(0, 9000), (50, 700), (51, 129)])
+    val = rng.standard_normal(col.size).astype(np.float32)
+    mat = rng.standard_normal((300, 64)).astype(np.float32)
+    exact = oracle.spmm(rowptr, col, val.astype(np.float64), mat.astype(np.float64))
+    cpu = oracle.spmm(rowptr, col, val, mat).astype(np.float64)
+    gpu = rt.spmm_func(cu(rowptr), cu(col), cu(val), cu(mat), "rowbalance_rowcache", None)
+    gpu = gpu.cpu().numpy().astype(np.float64)
+    err_cpu = np.abs(cpu - exact).max(axis=1)
+    err_gpu = np.abs(gpu - exact).max(axis=1)
+    scale = np.abs(exact).max(axis=1) + 1e-30
+    assert np.all(err_gpu <= 2 * err_cpu + 2e-7 * scale), (err_gpu / scale).max()
+
+
 def test_spmm_is_deterministic_and_reuses_its_plan(rt):
     rng = np.random.default_rng(5)
     rowptr, col = random_csr(rng, 2000, 1500, 40, long_rows=[(1, 5000), (77, 999)])
