@@ -1,0 +1,390 @@
+"""Benchmark of the compressed-propagation hot path (and, on request, of the cluster /
+reconstruct operators) on synthetic inputs.
+
+    python bench.py --gpus N --steps K --warmup W            # this package, N GPUs (torchrun for N>1)
+    python bench.py --impl reference --steps K --warmup W    # the reference's own CPU operators
+
+Default workload ("propagation"): compressed propagation SpMM, forward + transposed backward,
+on a seeded copying-model web graph with 325,557 nodes and ~3.2 M edges, features N x 256 fp32.
+One step = one forward and one backward pass over the whole graph.  The metric is
+original-edge x feature products per second: 2 * E_orig * F / t_step.
+
+Prints ONE JSON line (rank 0).  `value` is device-resident throughput (CUDA events, max over
+ranks); `e2e` goes through the public module API with pinned host buffers, copies included;
+`roofline` is for the dominant kernel (the fused vertex pass of the forward); `cpu_baseline`
+is the reference's CPU spmm_func chain on this host's cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "compressed_spmm_orig_edge_feat_per_s"
+UNIT = "Gedge*feat/s"
+
+
+# ---------------------------------------------------------------------------------------------
+# Workload construction (host side, untimed)
+# ---------------------------------------------------------------------------------------------
+WORKLOADS = {
+    # name: nodes, pareto x_min (sets E), feature width
+    "propagation": dict(n=325557, x_min=5.3, width=256, seed=2),
+    "propagation-small": dict(n=40000, x_min=5.3, width=256, seed=2),
+    "propagation-xl": dict(n=18500000, x_min=8.6, width=128, seed=4),
+}
+COMPRESS = dict(min_pair_frequency=4, threshold=4, max_depth=3, min_edge=1000000)
+
+
+def build_graph(name):
+    """Seeded copying-model graph -> CompressgnnData (self loops, symmetric normalisation,
+    grammar compression, block partition).  Stands in for the public web graphs the reference's
+    scripts load; nothing of those datasets is used."""
+    from compressgnn_b200 import offline as off
+    from compressgnn_b200.loader import CompressgnnData
+    w = WORKLOADS[name]
+    n = w["n"]
+    vlist, elist = off.generate_copy_graph(n, alpha=2.1, x_min=w["x_min"], max_degree=10000, copy_prob=0.7,
+                                           window=64, candidates=8, seed=w["seed"])
+    mask = np.ones(n, dtype=bool)
+    data = CompressgnnData(np.zeros((n, 1), np.float32), (vlist, elist), np.zeros(n, np.int64), mask, mask, mask,
+                           add_self_loop=True, normalize=True, graph_type="csr", **COMPRESS)
+    return data, int(elist.size)
+
+
+def block_bytes(block, width, rows_written, rows_accumulated, transposed=False):
+    """Algorithmic bytes of one SpMM block: every distinct source row read once, every output
+    row written once (and pre-read when accumulating), 4-byte column + 4-byte value per entry,
+    4-byte row pointers."""
+    rowptr, col, _val = block.csc() if transposed else block.csr()
+    distinct = int(np.unique(col.cpu().numpy()).size) if col.numel() else 0
+    return 4 * width * (rows_written + rows_accumulated + distinct) + 8 * col.numel() + 4 * rowptr.numel()
+
+
+def propagation_bytes(graph, width):
+    """Per-launch algorithmic bytes of the forward and backward passes."""
+    g = graph
+    n, r = g.vertex_cnt, g.rule_cnt
+    nonempty = lambda b, t=False: int(((b.csc() if t else b.csr())[0].diff() > 0).sum())
+    fwd = [("fwd_r2v", block_bytes(g.r2v_graph, width, r, 0))]
+    for i, lvl in enumerate(g.r2r_graph):
+        k = nonempty(lvl)
+        fwd.append((f"fwd_level{i}", block_bytes(lvl, width, k, k)))
+    fwd.append(("fwd_out", block_bytes(g.v2r_graph, width, n, 0) + block_bytes(g.v2v_graph, width, 0, 0)))
+    bwd = [("bwd_v2r_t", block_bytes(g.v2r_graph, width, r, 0, True))]
+    for i, lvl in reversed(list(enumerate(g.r2r_graph))):
+        k = nonempty(lvl, True)
+        bwd.append((f"bwd_level{i}", block_bytes(lvl, width, k, k, True)))
+    bwd.append(("bwd_out", block_bytes(g.v2v_graph, width, n, 0, True) + block_bytes(g.r2v_graph, width, 0, 0, True)))
+    return fwd, bwd
+
+
+# ---------------------------------------------------------------------------------------------
+# Clock sampling during the timed region
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.samples, self.proc, self.index = [], None, index
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6 and parts[0].isdigit():
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = sorted(int(s[0]) for s in self.samples)
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons,
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# Reference CPU arm / CPU baseline
+# ---------------------------------------------------------------------------------------------
+def cpu_propagation(data, width, steps, warmup, seed=0):
+    """The reference's CPU path: spmm_func(..., "rowbalance", ...) chained in the order of
+    layer/CompressgnnSPMM.py:47-53 (forward) and :80-85 (backward), all host threads.
+    Returns (seconds per step, kind, cores, sample description)."""
+    import torch
+    from oracle import oracle
+    rt, _off = oracle.reference_modules()
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = data.edge_index
+    n, r = g.vertex_cnt, g.rule_cnt
+    gen = torch.Generator().manual_seed(seed)
+    if rt is not None:
+        kind, sample_width = "reference", width
+    else:
+        kind, sample_width, cores = "port", min(width, 8), 1  # scalar single-thread C port: a column slice
+    x = torch.randn(n, sample_width, generator=gen)
+    grad = torch.randn(n, sample_width, generator=gen)
+    fwd_blocks = dict(r2v=g.r2v_graph.csr(), v2r=g.v2r_graph.csr(), v2v=g.v2v_graph.csr(),
+                      levels=[lvl.csr() for lvl in g.r2r_graph])
+    bwd_blocks = dict(v2r_t=g.v2r_graph.csc(), v2v_t=g.v2v_graph.csc(), r2v_t=g.r2v_graph.csc(),
+                      levels_t=[lvl.csc() for lvl in g.r2r_graph])
+
+    if rt is not None:
+        def spmm(blk, m, out=None):
+            return rt.spmm_func(blk[0], blk[1], blk[2], m, "rowbalance", out)
+    else:
+        def spmm(blk, m, out=None):
+            res = oracle.spmm(blk[0].numpy(), blk[1].numpy(), blk[2].numpy(), m.numpy(),
+                              None if out is None else out.numpy())
+            return torch.from_numpy(res)
+
+    def step():
+        rule_out = spmm(fwd_blocks["r2v"], x)
+        for lvl in fwd_blocks["levels"]:
+            rule_out = spmm(lvl, rule_out, rule_out)
+        out = spmm(fwd_blocks["v2v"], x, spmm(fwd_blocks["v2r"], rule_out))
+        rule_g = spmm(bwd_blocks["v2r_t"], grad)
+        for lvl in reversed(bwd_blocks["levels_t"]):
+            rule_g = spmm(lvl, rule_g, rule_g)
+        gx = spmm(bwd_blocks["r2v_t"], rule_g, spmm(bwd_blocks["v2v_t"], grad))
+        return out, gx
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    scale = width / sample_width  # a column slice scales linearly in the width
+    sample = (f"full workload, {steps} steps" if sample_width == width else
+              f"{sample_width} of {width} feature columns, {steps} steps, time scaled by {scale:g}")
+    return dt * scale, kind, cores, sample
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from compressgnn_b200.layer import Compressgnn_SPMM, spmm as spmm_layer
+    from compressgnn_b200 import runtime as rt
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    wl = WORKLOADS[args.workload]
+    width_total = wl["width"]
+    assert width_total % world == 0, "feature width must divide by the number of GPUs"
+    width = width_total // world  # column shard of this rank; the graph is replicated
+    data, e_orig = build_graph(args.workload)
+    cpu_graph_for_baseline = data if rank == 0 else None
+    graph = data.edge_index
+    n = graph.vertex_cnt
+
+    # CPU baseline first (rank 0, N=1 only), while the graph blocks are still host tensors.
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        sec, kind, cores, sample = cpu_propagation(cpu_graph_for_baseline, width_total, args.cpu_steps, 1)
+        cpu = {"value": 2 * e_orig * width_total / sec / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
+               "sample": sample, "ms_per_step": sec * 1e3}
+
+    fwd_bytes, bwd_bytes = propagation_bytes(graph, width)
+    graph.to(device)
+    gen = torch.Generator(device=device).manual_seed(1234 + rank)
+    x = torch.randn(n, width, device=device, generator=gen)
+    grad = torch.randn(n, width, device=device, generator=gen)
+    plan = graph.propagation_plan()
+    launches_per_step = 2 * (2 + graph.step)
+
+    def step(record=None):
+        out = spmm_layer._forward(graph, x, record)
+        gx = spmm_layer._backward(graph, grad, record)
+        return out, gx
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    records = []
+    with ClockSampler(local_rank) as clocks:
+        start.record()
+        for _ in range(args.steps):
+            rec = []
+            step(rec)
+            records.append(rec)
+        stop.record()
+        torch.cuda.synchronize()
+        # keep the GPU busy a little longer if the region was too short for one clock sample
+        t_end = time.time() + max(0.0, 0.6 - start.elapsed_time(stop) / 1e3)
+        while time.time() < t_end:
+            step()
+            torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+
+    # per-launch durations (events recorded inside the timed region)
+    per_launch = {}
+    for rec in records:
+        for name, e0, e1 in rec:
+            per_launch.setdefault(name, []).append(e0.elapsed_time(e1))
+    launch_ms = {k: float(np.mean(v)) for k, v in per_launch.items()}
+    bytes_by_name = dict(fwd_bytes + bwd_bytes)
+
+    # end to end through the public module API with pinned host buffers
+    module = Compressgnn_SPMM()
+    x_host = x.cpu().pin_memory()
+    g_host = grad.cpu().pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    gx_host = torch.empty_like(x_host).pin_memory()
+
+    def e2e_step():
+        xd = x_host.to(device, non_blocking=True).requires_grad_()
+        out = module(graph, xd)
+        out_host.copy_(out.detach(), non_blocking=True)
+        out.backward(g_host.to(device, non_blocking=True))
+        gx_host.copy_(xd.grad, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(2):
+        e2e_step()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_sec = (time.perf_counter() - t0) / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_sec], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_sec = float(t.item())
+
+    status = rt.device_status()
+    assert status == 0, f"device status word {status}"
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    if peaks_path.is_file():
+        peak, peak_src = json.loads(peaks_path.read_text())["hbm_gbs"], "measured (MEASURED_PEAKS.json)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    dom = "fwd_out"
+    achieved = bytes_by_name[dom] / (launch_ms[dom] * 1e-3) / 1e9
+    work = 2 * e_orig * width_total
+    line = {
+        "metric": METRIC, "value": work / (ms_per_step * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: compressed propagation SpMM fwd+bwd, copying-model web graph",
+                   "nodes": n, "orig_edges": e_orig, "compressed_edges": graph.edge_count(),
+                   "rules": graph.rule_cnt, "levels": graph.step, "feature_width": width_total,
+                   "columns_per_gpu": width, "compressor": COMPRESS,
+                   "l2": "inputs larger than L2 (X is %.0f MB per GPU)" % (4e-6 * n * width),
+                   "parallelism": f"feature columns sharded over {world} GPU(s), graph replicated, no collective"},
+        "e2e": {"value": work / e2e_sec / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * 4 * n * width,
+                "d2h_bytes_per_step": 2 * 4 * n * width, "ms_per_step": e2e_sec * 1e3},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "kernel": "seg_kernel (fused v2r+v2v vertex pass, forward)",
+                     "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": peak_src, "traffic": None,
+                     "algorithmic_bytes_per_launch": bytes_by_name[dom], "ms_per_launch": launch_ms[dom],
+                     "launches": {k: {"ms": launch_ms[k], "algorithmic_GBps": bytes_by_name[k] / launch_ms[k] / 1e6}
+                                  for k in launch_ms}},
+        "clocks": clocks.summary(),
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the same workload, on this box's host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = WORKLOADS[args.workload]
+    data, e_orig = build_graph(args.workload)
+    sec, kind, cores, sample = cpu_propagation(data, wl["width"], args.steps, min(args.warmup, 2))
+    value = 2 * e_orig * wl["width"] / sec / 1e9
+    g = data.edge_index
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
+        "steps": args.steps, "warmup": min(args.warmup, 2), "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: compressed propagation SpMM fwd+bwd, copying-model web graph",
+                   "nodes": g.vertex_cnt, "orig_edges": e_orig, "compressed_edges": g.edge_count(),
+                   "rules": g.rule_cnt, "levels": g.step, "feature_width": wl["width"], "compressor": COMPRESS},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["cgnn", "reference"], default="cgnn")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="propagation")
+    ap.add_argument("--cpu-steps", type=int, default=3, help="steps of the CPU baseline leg")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

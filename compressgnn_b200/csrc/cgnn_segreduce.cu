@@ -2,10 +2,13 @@
 //
 // One kernel serves the compressed-propagation SpMM blocks, the fused two-block pass, the
 // per-bucket mean and the reconstruct backward.  Design points (B200, HBM-bound):
-//   * a row is owned by a group of LPR lanes; every lane keeps VPL 16-byte vectors of the
-//     row in registers, so one gathered feature row is LPR*VPL coalesced 128-bit loads;
-//   * the group reads LPR (col,val) pairs with one coalesced load and broadcasts them by
-//     shuffle; U gathered rows are in flight per lane before the FMAs are issued;
+//   * a group of LPR lanes owns up to LPR consecutive rows; every lane keeps VPL 16-byte
+//     vectors of the current row in registers, so one gathered feature row is LPR*VPL
+//     coalesced 128-bit loads;
+//   * the entries of the group's rows are read as one stream: LPR (col,val) pairs per
+//     coalesced load (the next batch is requested before the current one is consumed),
+//     broadcast by shuffle; U gathered rows are in flight per lane before the FMAs issue,
+//     across row boundaries;
 //   * rows longer than `split` are cut into chunks (work units of their own); a chunk
 //     writes its partial sum to scratch, takes a ticket, and the chunk that draws the last
 //     ticket adds the partials in chunk order -- deterministic, no float atomics, and no
@@ -15,9 +18,51 @@
 
 #include "cgnn_plan.h"
 
+// Build-time tuning knobs (defaults are the measured best; see profiles/).
+#ifndef CGNN_SEG_USCALE
+#define CGNN_SEG_USCALE 8   // 16-byte gather loads a lane keeps in flight
+#endif
+#ifndef CGNN_SEG_LDMODE
+#define CGNN_SEG_LDMODE 0   // 0 plain ld.global, 1 ld.global.cg (bypass L1), 2 ld.global.nc
+#endif
+#ifndef CGNN_SEG_RPU
+#define CGNN_SEG_RPU 8      // rows per direct work unit (capped by the lane-group width)
+#endif
+#ifndef CGNN_SEG_STREAMHINT
+#define CGNN_SEG_STREAMHINT 0  // 1: evict-first loads of indices and streaming stores of rows
+#endif
+#ifndef CGNN_SEG_THREADS
+#define CGNN_SEG_THREADS 128
+#endif
+#ifndef CGNN_SEG_MINBLOCKS
+#define CGNN_SEG_MINBLOCKS 6
+#endif
+
 namespace cgnn {
 
 static __device__ int g_seg_status = 0;
+
+template <typename T, int VW>
+__device__ __forceinline__ Vec<T, VW> gather_load(const T *p) {
+#if CGNN_SEG_LDMODE == 1
+    return vec_load_cg<T, VW>(p);
+#elif CGNN_SEG_LDMODE == 2
+    Vec<T, VW> r;
+    if constexpr (sizeof(T) * VW == 16) {
+        float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+        r = *reinterpret_cast<Vec<T, VW> *>(&t);
+    } else if constexpr (sizeof(T) * VW == 8) {
+        float2 t = __ldg(reinterpret_cast<const float2 *>(p));
+        r = *reinterpret_cast<Vec<T, VW> *>(&t);
+    } else {
+        float t = __ldg(reinterpret_cast<const float *>(p));
+        r = *reinterpret_cast<Vec<T, VW> *>(&t);
+    }
+    return r;
+#else
+    return vec_load<T, VW>(p);
+#endif
+}
 
 int segreduce_status(int *out) {
     int zero = 0;
@@ -48,140 +93,12 @@ struct SegArgs {
     int *tickets;
 };
 
-template <typename T, int VW, int LPR, int VPL, int U, bool MASKED>
-__device__ __forceinline__ void gather_edges(Vec<T, VW> (&acc)[VPL], const int32_t *col,
-                                             const T *val, const T *src, const T *mask,
-                                             int64_t width, int64_t colbase,
-                                             const bool (&colok)[VPL], int e0, int e1, int gl,
-                                             unsigned gmask) {
+// Store (or accumulate, or divide) one finished row.
+template <typename T, int VW, int LPR, int VPL>
+__device__ __forceinline__ void finish_row(const SegArgs<T> &a, int32_t row, Vec<T, VW> (&acc)[VPL],
+                                           int64_t colbase, const bool (&colok)[VPL]) {
     using V = Vec<T, VW>;
-    for (int base = e0; base < e1; base += LPR) {
-        const int mine = base + gl;
-        int c = 0;
-        T v = T(0);
-        if (mine < e1) {
-            c = col[mine];
-            v = val ? val[mine] : T(1);
-        }
-        const int cnt = min(LPR, e1 - base);
-        for (int j = 0; j < cnt; j += U) {
-            V x[U][VPL];
-            T w[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int cj = __shfl_sync(gmask, c, j + u, LPR);
-                w[u] = __shfl_sync(gmask, v, j + u, LPR);
-                if (j + u < cnt) {
-                    const int64_t off = (int64_t)cj * width + colbase;
-#pragma unroll
-                    for (int p = 0; p < VPL; ++p) {
-                        if (colok[p]) {
-                            x[u][p] = vec_load<T, VW>(src + off + p * (LPR * VW));
-                            if constexpr (MASKED) {
-                                const V m = vec_load<T, VW>(mask + off + p * (LPR * VW));
-#pragma unroll
-                                for (int i = 0; i < VW; ++i)
-                                    if (m.v[i] <= T(0)) x[u][p].v[i] = T(0);
-                            }
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (j + u < cnt) {
-#pragma unroll
-                    for (int p = 0; p < VPL; ++p) {
-                        if (colok[p]) {
-#pragma unroll
-                            for (int i = 0; i < VW; ++i)
-                                acc[p].v[i] = fma(x[u][p].v[i], w[u], acc[p].v[i]);
-                        }
-                    }
-                }
-            }
-        }
-    }
-}
-
-template <typename T, int VW, int LPR, int VPL, bool MASKED>
-__global__ void __launch_bounds__(256) seg_kernel(const SegArgs<T> a) {
-    using V = Vec<T, VW>;
-    constexpr int GPW = 32 / LPR;
-    constexpr int U0 = VPL >= 8 ? 1 : 8 / VPL;
-    constexpr int U = U0 < LPR ? U0 : LPR;
-    const int lane = threadIdx.x & 31;
-    const int gl = lane & (LPR - 1);
-    const unsigned gmask =
-        LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (lane & ~(LPR - 1)));
-    const int64_t g =
-        ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * GPW + lane / LPR;
-    const int64_t width = a.width;
-    const int64_t colbase = (int64_t)blockIdx.y * (LPR * VPL * VW) + gl * VW;
-    bool colok[VPL];
-    V acc[VPL];
-#pragma unroll
-    for (int p = 0; p < VPL; ++p) {
-        colok[p] = colbase + p * (LPR * VW) < width;
-        acc[p] = vec_zero<T, VW>();
-    }
-
-    int32_t row;
-    if (g < a.n_direct) {
-        row = a.row_ids ? a.row_ids[g] : (int32_t)g;
-        const int a0 = a.rowptr[0][row], a1 = a.rowptr[0][row + 1];
-        int b0 = 0, b1 = 0;
-        if (a.nterms > 1) {
-            b0 = a.rowptr[1][row];
-            b1 = a.rowptr[1][row + 1];
-        }
-        if ((a1 - a0) + (b1 - b0) > a.split) return;  // cut into chunks; see below
-        gather_edges<T, VW, LPR, VPL, U, MASKED>(acc, a.col[0], a.val[0], a.src[0], a.mask_src,
-                                                 width, colbase, colok, a0, a1, gl, gmask);
-        if (a.nterms > 1)
-            gather_edges<T, VW, LPR, VPL, U, MASKED>(acc, a.col[1], a.val[1], a.src[1],
-                                                     a.mask_src, width, colbase, colok, b0, b1,
-                                                     gl, gmask);
-    } else {
-        const int64_t it = g - a.n_direct;
-        if (it >= a.n_items) return;
-        const int4 item = a.items[it];
-        const int t = item.y;
-        gather_edges<T, VW, LPR, VPL, U, MASKED>(acc, a.col[t], a.val[t], a.src[t], a.mask_src,
-                                                 width, colbase, colok, item.z, item.w, gl,
-                                                 gmask);
-        const int4 lr = a.longs[item.x];
-        T *part = a.partial + it * width + colbase;
-#pragma unroll
-        for (int p = 0; p < VPL; ++p)
-            if (colok[p]) vec_store<T, VW>(part + p * (LPR * VW), acc[p]);
-        __threadfence();
-        __syncwarp(gmask);
-        int *tk = a.tickets + (int64_t)item.x * gridDim.y + blockIdx.y;
-        int ticket = 0;
-        if (gl == 0) ticket = atomicAdd(tk, 1);
-        ticket = __shfl_sync(gmask, ticket, 0, LPR);
-        if (ticket != lr.z - 1) return;
-        // Last chunk of this row (for this column tile): add the partials in chunk order.
-        __threadfence();
-#pragma unroll
-        for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
-        for (int s = 0; s < lr.z; ++s) {
-            const T *ps = a.partial + (int64_t)(lr.y + s) * width + colbase;
-#pragma unroll
-            for (int p = 0; p < VPL; ++p) {
-                if (colok[p]) {
-                    const V q = vec_load_cg<T, VW>(ps + p * (LPR * VW));
-#pragma unroll
-                    for (int i = 0; i < VW; ++i) acc[p].v[i] += q.v[i];
-                }
-            }
-        }
-        if (gl == 0) *tk = 0;  // leave the ticket ready for the next launch
-        row = lr.x;
-    }
-
-    T *orow = a.out + (int64_t)row * width + colbase;
+    T *orow = a.out + (int64_t)row * a.width + colbase;
     T divisor = T(1);
     const bool divide = a.div_counts != nullptr;
     if (divide) divisor = (T)max(a.div_counts[row], 1);
@@ -198,19 +115,234 @@ __global__ void __launch_bounds__(256) seg_kernel(const SegArgs<T> a) {
 #pragma unroll
                 for (int i = 0; i < VW; ++i) r.v[i] = r.v[i] / divisor;
             }
+#if CGNN_SEG_STREAMHINT
+            vec_store_cs<T, VW>(orow + p * (LPR * VW), r);
+#else
             vec_store<T, VW>(orow + p * (LPR * VW), r);
+#endif
         }
     }
 }
 
+// One work unit per group of LPR lanes: either up to LPR rows of the direct row list (their
+// entries are streamed as ONE sequence, so the loads of a row's gathered feature rows are in
+// flight together with its neighbours' and a short row costs no pipeline restart), or one
+// chunk of a long row.  Lane q of the group keeps the extent of row slot q; an entry's slot is
+// found by a shuffle binary search over the slots' prefix sums.
+template <typename T, int VW, int LPR, int VPL, bool MASKED>
+__global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kernel(const SegArgs<T> a) {
+    using V = Vec<T, VW>;
+    constexpr int GPW = 32 / LPR;
+    constexpr int U0 = VPL >= CGNN_SEG_USCALE ? 1 : CGNN_SEG_USCALE / VPL;
+    constexpr int U = U0 < LPR ? U0 : LPR;
+    const int lane = threadIdx.x & 31;
+    const int gl = lane & (LPR - 1);
+    const unsigned gmask =
+        LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (lane & ~(LPR - 1)));
+    const int64_t unit =
+        ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * GPW + lane / LPR;
+    const int64_t width = a.width;
+    const int64_t colbase = (int64_t)blockIdx.y * (LPR * VPL * VW) + gl * VW;
+    bool colok[VPL];
+    V acc[VPL];
+#pragma unroll
+    for (int p = 0; p < VPL; ++p) {
+        colok[p] = colbase + p * (LPR * VW) < width;
+        acc[p] = vec_zero<T, VW>();
+    }
+
+    // ---- row slots of this unit -------------------------------------------------------
+    constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR;
+    const int64_t direct_units = (a.n_direct + RPU - 1) / RPU;
+    int my_row = 0, s0 = 0, d0 = 0, s1 = 0, d1 = 0;
+    bool my_write = false;
+    int nr;
+    int64_t item_index = -1;
+    int4 lr = make_int4(0, 0, 0, 0);
+    int long_index = 0;
+    if (unit < direct_units) {
+        const int64_t first = unit * RPU;
+        nr = (int)min((int64_t)RPU, a.n_direct - first);
+        if (gl < nr) {
+            my_row = a.row_ids ? a.row_ids[first + gl] : (int32_t)(first + gl);
+            s0 = a.rowptr[0][my_row];
+            d0 = a.rowptr[0][my_row + 1] - s0;
+            if (a.nterms > 1) {
+                s1 = a.rowptr[1][my_row];
+                d1 = a.rowptr[1][my_row + 1] - s1;
+            }
+            my_write = d0 + d1 <= a.split;  // longer rows are served by chunk units
+            if (!my_write) d0 = d1 = 0;
+        }
+    } else {
+        item_index = unit - direct_units;
+        if (item_index >= a.n_items) return;
+        const int4 item = a.items[item_index];
+        long_index = item.x;
+        lr = a.longs[item.x];
+        nr = 1;
+        if (gl == 0) {
+            my_row = lr.x;
+            if (item.y == 0) {
+                s0 = item.z;
+                d0 = item.w - item.z;
+            } else {
+                s1 = item.z;
+                d1 = item.w - item.z;
+            }
+        }
+    }
+    // exclusive prefix of the slot lengths inside the group
+    const int deg = d0 + d1;
+    int incl = deg;
+#pragma unroll
+    for (int o = 1; o < LPR; o <<= 1) {
+        const int t = __shfl_up_sync(gmask, incl, o, LPR);
+        if (gl >= o) incl += t;
+    }
+    const int P = incl - deg;
+    const int total = __shfl_sync(gmask, incl, LPR - 1, LPR);
+
+    // entry k of the unit's stream -> (column, value, slot | term << 8)
+    auto fetch = [&](int k, int &c, T &v, int &qt) {
+        int q = 0;
+#pragma unroll
+        for (int step = LPR / 2; step >= 1; step >>= 1) {
+            const int cand = q + step;
+            const int pc = __shfl_sync(gmask, P, cand & (LPR - 1), LPR);
+            if (cand < nr && pc <= k) q = cand;
+        }
+        const int pq = __shfl_sync(gmask, P, q, LPR);
+        const int s0q = __shfl_sync(gmask, s0, q, LPR);
+        const int d0q = __shfl_sync(gmask, d0, q, LPR);
+        const int s1q = __shfl_sync(gmask, s1, q, LPR);
+        c = 0;
+        v = T(0);
+        qt = q;
+        if (k < total) {
+            const int o = k - pq;
+            const int term = o >= d0q ? 1 : 0;
+            const int e = term ? s1q + (o - d0q) : s0q + o;
+            const T *vp = a.val[term];
+#if CGNN_SEG_STREAMHINT
+            c = __ldcs(a.col[term] + e);
+            v = vp ? __ldcs(vp + e) : T(1);
+#else
+            c = a.col[term][e];
+            v = vp ? vp[e] : T(1);
+#endif
+            qt = q | (term << 8);
+        }
+    };
+
+    int cur = 0;  // slot whose sum is in acc
+    auto flush_until = [&](int upto) {  // finish slots cur .. upto-1 (all but the first are empty)
+        for (; cur < upto; ++cur) {
+            const int row = __shfl_sync(gmask, my_row, cur, LPR);
+            const int wr = __shfl_sync(gmask, (int)my_write, cur, LPR);
+            if (wr) finish_row<T, VW, LPR, VPL>(a, row, acc, colbase, colok);
+#pragma unroll
+            for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
+        }
+    };
+
+    int c, qt, c_next = 0, qt_next = 0;
+    T v, v_next = T(0);
+    fetch(gl, c, v, qt);
+    for (int base = 0; base < total; base += LPR) {
+        if (base + LPR < total) fetch(base + LPR + gl, c_next, v_next, qt_next);
+        const int cnt = min(LPR, total - base);
+        for (int j = 0; j < cnt; j += U) {
+            V x[U][VPL];
+            T w[U];
+            int slot[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int cj = __shfl_sync(gmask, c, j + u, LPR);
+                w[u] = __shfl_sync(gmask, v, j + u, LPR);
+                slot[u] = __shfl_sync(gmask, qt, j + u, LPR);
+                if (j + u < cnt) {
+                    const T *src = (slot[u] >> 8) ? a.src[1] : a.src[0];
+                    const int64_t off = (int64_t)cj * width + colbase;
+#pragma unroll
+                    for (int p = 0; p < VPL; ++p) {
+                        if (colok[p]) {
+                            x[u][p] = gather_load<T, VW>(src + off + p * (LPR * VW));
+                            if constexpr (MASKED) {
+                                const V m = vec_load<T, VW>(a.mask_src + off + p * (LPR * VW));
+#pragma unroll
+                                for (int i = 0; i < VW; ++i)
+                                    if (m.v[i] <= T(0)) x[u][p].v[i] = T(0);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (j + u < cnt) {
+                    const int q = slot[u] & 0xff;
+                    if (q != cur) flush_until(q);
+#pragma unroll
+                    for (int p = 0; p < VPL; ++p) {
+                        if (colok[p]) {
+#pragma unroll
+                            for (int i = 0; i < VW; ++i)
+                                acc[p].v[i] = fma(x[u][p].v[i], w[u], acc[p].v[i]);
+                        }
+                    }
+                }
+            }
+        }
+        c = c_next;
+        v = v_next;
+        qt = qt_next;
+    }
+
+    if (item_index < 0) {
+        flush_until(nr);
+        return;
+    }
+
+    // ---- chunk of a long row: publish the partial sum, last ticket adds them up ---------
+    T *part = a.partial + item_index * width + colbase;
+#pragma unroll
+    for (int p = 0; p < VPL; ++p)
+        if (colok[p]) vec_store<T, VW>(part + p * (LPR * VW), acc[p]);
+    __threadfence();
+    __syncwarp(gmask);
+    int *tk = a.tickets + (int64_t)long_index * gridDim.y + blockIdx.y;
+    int ticket = 0;
+    if (gl == 0) ticket = atomicAdd(tk, 1);
+    ticket = __shfl_sync(gmask, ticket, 0, LPR);
+    if (ticket != lr.z - 1) return;
+    __threadfence();
+#pragma unroll
+    for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
+    for (int s = 0; s < lr.z; ++s) {
+        const T *ps = a.partial + (int64_t)(lr.y + s) * width + colbase;
+#pragma unroll
+        for (int p = 0; p < VPL; ++p) {
+            if (colok[p]) {
+                const V q = vec_load_cg<T, VW>(ps + p * (LPR * VW));
+#pragma unroll
+                for (int i = 0; i < VW; ++i) acc[p].v[i] += q.v[i];
+            }
+        }
+    }
+    if (gl == 0) *tk = 0;  // leave the ticket ready for the next launch
+    finish_row<T, VW, LPR, VPL>(a, lr.x, acc, colbase, colok);
+}
+
 template <typename T, int VW, int LPR, int VPL, bool MASKED>
 static int launch_cfg(const SegArgs<T> &a, cudaStream_t stream) {
-    const int64_t groups = a.n_direct + a.n_items;
-    const int64_t per_block = 8 * (32 / LPR);
-    const int64_t gx = ceil_div(groups, per_block);
+    constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR;
+    const int64_t units = ceil_div(a.n_direct, RPU) + a.n_items;
+    const int64_t per_block = (CGNN_SEG_THREADS / 32) * (32 / LPR);
+    const int64_t gx = ceil_div(units, per_block);
     const int64_t gy = ceil_div(a.width, (int64_t)LPR * VPL * VW);
     CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
-    seg_kernel<T, VW, LPR, VPL, MASKED><<<dim3((unsigned)gx, (unsigned)gy), 256, 0, stream>>>(a);
+    seg_kernel<T, VW, LPR, VPL, MASKED><<<dim3((unsigned)gx, (unsigned)gy), CGNN_SEG_THREADS, 0, stream>>>(a);
     CGNN_LAUNCH_CHECK();
     return CGNN_OK;
 }

@@ -20,28 +20,46 @@ def _require_cuda(x):
         raise RuntimeError("compressgnn_b200 runs on CUDA tensors only (no CPU propagation path)")
 
 
-def _forward(graph, x):
+def _timed(record, name, launch):
+    """Run one launch; with a ``record`` list, bracket it with CUDA events on the current
+    stream and append ``(name, start, stop)`` (used by the benchmark's per-kernel timing)."""
+    if record is None:
+        return launch()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    result = launch()
+    stop.record()
+    record.append((name, start, stop))
+    return result
+
+
+def _forward(graph, x, record=None):
     _require_cuda(x)
     x = x.contiguous()
     plan = graph.propagation_plan()
     dt = x.dtype
-    rule_out = _native.spmm_with_plan(plan.r2v, graph.r2v_graph.value_as(dt), x)
-    for level_plan, level in zip(plan.levels, graph.r2r_graph):
-        _native.spmm_with_plan(level_plan, level.value_as(dt), rule_out, out=rule_out, accumulate=True)
-    return _native.spmm_pair_with_plan(plan.out, graph.v2r_graph.value_as(dt), rule_out,
-                                       graph.v2v_graph.value_as(dt), x)
+    rule_out = _timed(record, "fwd_r2v", lambda: _native.spmm_with_plan(
+        plan.r2v, graph.r2v_graph.value_as(dt), x))
+    for i, (level_plan, level) in enumerate(zip(plan.levels, graph.r2r_graph)):
+        _timed(record, f"fwd_level{i}", lambda: _native.spmm_with_plan(
+            level_plan, level.value_as(dt), rule_out, out=rule_out, accumulate=True))
+    return _timed(record, "fwd_out", lambda: _native.spmm_pair_with_plan(
+        plan.out, graph.v2r_graph.value_as(dt), rule_out, graph.v2v_graph.value_as(dt), x))
 
 
-def _backward(graph, grad):
+def _backward(graph, grad, record=None):
     _require_cuda(grad)
     grad = grad.contiguous()
     plan = graph.propagation_plan()
     dt = grad.dtype
-    rule_out = _native.spmm_with_plan(plan.v2r_t, graph.v2r_graph.value_as(dt, True), grad)
-    for level_plan, level in zip(reversed(plan.levels_t), reversed(graph.r2r_graph)):
-        _native.spmm_with_plan(level_plan, level.value_as(dt, True), rule_out, out=rule_out, accumulate=True)
-    return _native.spmm_pair_with_plan(plan.out_t, graph.v2v_graph.value_as(dt, True), grad,
-                                       graph.r2v_graph.value_as(dt, True), rule_out)
+    rule_out = _timed(record, "bwd_v2r_t", lambda: _native.spmm_with_plan(
+        plan.v2r_t, graph.v2r_graph.value_as(dt, True), grad))
+    levels = list(enumerate(zip(plan.levels_t, graph.r2r_graph)))
+    for i, (level_plan, level) in reversed(levels):
+        _timed(record, f"bwd_level{i}", lambda: _native.spmm_with_plan(
+            level_plan, level.value_as(dt, True), rule_out, out=rule_out, accumulate=True))
+    return _timed(record, "bwd_out", lambda: _native.spmm_pair_with_plan(
+        plan.out_t, graph.v2v_graph.value_as(dt, True), grad, graph.r2v_graph.value_as(dt, True), rule_out))
 
 
 def compress_spmm(graph, x_j):
