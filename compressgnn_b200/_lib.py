@@ -45,7 +45,7 @@ SIGNATURES = {
     "cgnn_cluster_mean": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
                                    _c_size, _c_ptr]),
     "cgnn_cluster_mean_backward": (_c_int, [_c_int, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr,
-                                            _c_ptr, _c_ptr, _c_ptr]),
+                                            _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
     "cgnn_cluster_reconstruct": (_c_int, [_c_int, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr,
                                           _c_int, _c_ptr, _c_ptr]),
     "cgnn_cluster_reconstruct_backward": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_int,

@@ -29,12 +29,16 @@ int cluster_status(int *out) {
 }
 
 constexpr int PROJ_THREADS = 128;
-constexpr int KC = 32;        // columns per pipeline stage
-constexpr int XS_STRIDE = 36; // padded row stride of the X stage (elements)
+constexpr int KC = 16;         // columns per pipeline stage
+constexpr int XS_STRIDE = 20;  // padded row stride of the X stage (elements): odd in 16-byte units
+constexpr int PROJ_CTAS_PER_SM = 5;  // 43 KB of shared memory per CTA at 16 planes
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem, int src_bytes) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem),
+    // .L2::256B: the 64-byte slice of a feature row this stage needs pulls the surrounding
+    // 256 bytes into L2, so the following k-stages of the same rows hit L2 and DRAM sees
+    // whole-page bursts instead of scattered 64-byte reads.
+    asm volatile("cp.async.cg.shared.global.L2::256B [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem),
                  "r"(src_bytes)
                  : "memory");
 }
@@ -52,21 +56,39 @@ struct ProjSmem {
 };
 
 // Stage loader: X[row0 .. row0+TR, k0 .. k0+KC) and planes[k0 .. k0+KC, 0..bits) -> shared,
-// zero-filled outside the matrix.  The vector path needs 16-byte aligned rows.
+// zero-filled outside the matrix.  On the vector path (16-byte aligned rows) a thread always
+// moves the same 16-byte column slot of rows (t / VPR) + j * (THREADS / VPR), so its global
+// and shared offsets are a fixed base plus a constant stride per j: a handful of integer
+// instructions per 16-byte cp.async instead of a div/mod per element.
 template <typename T, int HB, int RPT>
 __device__ __forceinline__ void load_stage(ProjSmem<T, HB, RPT> &sm, int stage, const T *x,
                                            const T *planes, int64_t n, int64_t width, int bits,
                                            int64_t row0, int64_t k0, bool vec_ok) {
     constexpr int TR = PROJ_THREADS * RPT;
     constexpr int VW = 16 / (int)sizeof(T);
-    constexpr int VPR = KC / VW;  // vectors per row of the stage
+    constexpr int VPR = KC / VW;                   // 16-byte slots per row of the stage
+    constexpr int ROWS_PER_PASS = PROJ_THREADS / VPR;
+    constexpr int PASSES = TR / ROWS_PER_PASS;
     if (vec_ok) {
-        for (int i = threadIdx.x; i < TR * VPR; i += PROJ_THREADS) {
-            const int r = i / VPR, c = (i % VPR) * VW;
-            const int64_t gr = row0 + r, gk = k0 + c;
-            const bool ok = gr < n && gk < width;  // width % VW == 0 on this path
-            cp_async16(&sm.xs[stage][r][c], ok ? (const void *)(x + gr * width + gk) : (const void *)x,
+        const int r0 = threadIdx.x / VPR, c = (threadIdx.x % VPR) * VW;
+        const bool col_ok = k0 + c < width;  // width % VW == 0 on this path
+        const T *g = x + (row0 + r0) * width + k0 + c;
+        T *sdst = &sm.xs[stage][r0][c];
+        const int64_t rows_left = n - row0 - r0;
+#pragma unroll
+        for (int j = 0; j < PASSES; ++j) {
+            const bool ok = col_ok && (int64_t)j * ROWS_PER_PASS < rows_left;
+            cp_async16(sdst + j * (ROWS_PER_PASS * XS_STRIDE),
+                       ok ? (const void *)(g + (int64_t)j * ROWS_PER_PASS * width) : (const void *)x,
                        ok ? 16 : 0);
+        }
+        if (bits == HB && k0 + KC <= width) {
+            // the KC plane rows of this stage are one contiguous block of KC*HB elements
+            constexpr int SLOTS = KC * HB / VW;
+            const T *pg = planes + k0 * HB;
+            T *ps = &sm.ws[stage][0][0];
+            for (int i = threadIdx.x; i < SLOTS; i += PROJ_THREADS) cp_async16(ps + i * VW, pg + i * VW, 16);
+            return;
         }
     } else {
         for (int i = threadIdx.x; i < TR * KC; i += PROJ_THREADS) {
@@ -174,9 +196,12 @@ static int launch_project(const T *x, const T *planes, int64_t n, int64_t width,
     const size_t smem = sizeof(Smem);
     auto kernel = project_kernel<T, HB, RPT>;
     CGNN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CGNN_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                   cudaSharedmemCarveoutMaxShared));
     const int64_t tiles = ceil_div(n, TR);
-    const int64_t grid = std::min<int64_t>(tiles, 148 * 2);
-    const bool vec_ok = width % VW == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    const int64_t grid = std::min<int64_t>(tiles, 148 * PROJ_CTAS_PER_SM);
+    const bool vec_ok = width % VW == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                        (reinterpret_cast<uintptr_t>(planes) & 15) == 0;
     kernel<<<(unsigned)grid, PROJ_THREADS, smem, stream>>>(x, planes, n, width, bits, proj, codes,
                                                           vec_ok ? 1 : 0);
     CGNN_LAUNCH_CHECK();

@@ -85,6 +85,16 @@ __global__ void __launch_bounds__(256) expand_kernel(const ExpandArgs<T> a) {
     }
 }
 
+// table[g,:] / max(count[g],1) for the (small) group table, one thread per element.
+template <typename T>
+__global__ void scale_rows_kernel(const T *table, const int32_t *count, T *out, int64_t groups,
+                                  int64_t width) {
+    const int64_t total = groups * width;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)blockDim.x * gridDim.x)
+        out[i] = table[i] / (T)max(count[i / width], 1);
+}
+
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <typename T, int VW, int LPR>
@@ -143,9 +153,23 @@ extern "C" {
 
 int cgnn_cluster_mean_backward(int dtype, int64_t n, int64_t width, int64_t groups,
                                const void *grad, const int64_t *index, const int32_t *count,
-                               void *out, cgnn_stream_t stream) {
+                               void *out, void *scaled, cgnn_stream_t stream) {
     CGNN_REQUIRE(count != nullptr || n == 0, "mean_backward: null counts");
-    return expand(dtype, n, width, groups, grad, index, nullptr, count, 0, out,
+    CGNN_REQUIRE(dtype == CGNN_F32 || dtype == CGNN_F64, "gather: unknown dtype %d", dtype);
+    if (scaled == nullptr || n == 0 || width == 0 || groups == 0)
+        return expand(dtype, n, width, groups, grad, index, nullptr, count, 0, out,
+                      (cudaStream_t)stream);
+    CGNN_REQUIRE(grad != nullptr, "mean_backward: null gradient");
+    const int64_t total = groups * width;
+    const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(total, 256), 148 * 8);
+    if (dtype == CGNN_F32)
+        scale_rows_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+            (const float *)grad, count, (float *)scaled, groups, width);
+    else
+        scale_rows_kernel<double><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+            (const double *)grad, count, (double *)scaled, groups, width);
+    CGNN_LAUNCH_CHECK();
+    return expand(dtype, n, width, groups, scaled, index, nullptr, nullptr, 0, out,
                   (cudaStream_t)stream);
 }
 

@@ -35,7 +35,7 @@
 #define CGNN_SEG_THREADS 128
 #endif
 #ifndef CGNN_SEG_MINBLOCKS
-#define CGNN_SEG_MINBLOCKS 6
+#define CGNN_SEG_MINBLOCKS 5
 #endif
 
 namespace cgnn {
@@ -79,6 +79,8 @@ struct SegArgs {
     const T *src[2];
     int nterms;
     const T *mask_src;          // MASKED: entries whose mask_src value is <= 0 contribute 0
+    const T *seg_mask;          // optional: the finished row is zeroed where the mask row of its
+                                // FIRST entry is <= 0 (all entries of a row share one mask row)
     const int32_t *div_counts;  // optional: divide the row by max(div_counts[row], 1)
     T *out;
     int accumulate;
@@ -93,12 +95,85 @@ struct SegArgs {
     int *tickets;
 };
 
+// Sum of one contiguous entry range [e0, e1) of one block into acc: LPR (col,val) pairs per
+// coalesced load, U gathered rows in flight per lane.  Used for the chunks of long rows.
+template <typename T, int VW, int LPR, int VPL, int U, bool MASKED>
+__device__ __forceinline__ void gather_range(Vec<T, VW> (&acc)[VPL], const int32_t *col,
+                                             const T *val, const T *src, const T *mask,
+                                             int64_t width, int64_t colbase,
+                                             const bool (&colok)[VPL], int e0, int e1, int gl,
+                                             unsigned gmask) {
+    using V = Vec<T, VW>;
+    for (int base = e0; base < e1; base += LPR) {
+        const int mine = base + gl;
+        int c = 0;
+        T v = T(0);
+        if (mine < e1) {
+            c = col[mine];
+            v = val ? val[mine] : T(1);
+        }
+        const int cnt = min(LPR, e1 - base);
+        for (int j = 0; j < cnt; j += U) {
+            V x[U][VPL];
+            T w[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int cj = __shfl_sync(gmask, c, j + u, LPR);
+                w[u] = __shfl_sync(gmask, v, j + u, LPR);
+                if (j + u < cnt) {
+                    const int64_t off = (int64_t)cj * width + colbase;
+#pragma unroll
+                    for (int p = 0; p < VPL; ++p) {
+                        if (colok[p]) {
+                            x[u][p] = gather_load<T, VW>(src + off + p * (LPR * VW));
+                            if constexpr (MASKED) {
+                                const V m = vec_load<T, VW>(mask + off + p * (LPR * VW));
+#pragma unroll
+                                for (int i = 0; i < VW; ++i)
+                                    if (m.v[i] <= T(0)) x[u][p].v[i] = T(0);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                if (j + u < cnt) {
+#pragma unroll
+                    for (int p = 0; p < VPL; ++p) {
+                        if (colok[p]) {
+#pragma unroll
+                            for (int i = 0; i < VW; ++i)
+                                acc[p].v[i] = fma(x[u][p].v[i], w[u], acc[p].v[i]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
 // Store (or accumulate, or divide) one finished row.
 template <typename T, int VW, int LPR, int VPL>
 __device__ __forceinline__ void finish_row(const SegArgs<T> &a, int32_t row, Vec<T, VW> (&acc)[VPL],
                                            int64_t colbase, const bool (&colok)[VPL]) {
     using V = Vec<T, VW>;
     T *orow = a.out + (int64_t)row * a.width + colbase;
+    if (a.seg_mask) {
+        const int first = a.rowptr[0][row];
+        if (first < a.rowptr[0][row + 1]) {
+            const T *mrow = a.seg_mask + (int64_t)a.col[0][first] * a.width + colbase;
+#pragma unroll
+            for (int p = 0; p < VPL; ++p) {
+                if (colok[p]) {
+                    const V m = vec_load<T, VW>(mrow + p * (LPR * VW));
+#pragma unroll
+                    for (int i = 0; i < VW; ++i)
+                        if (m.v[i] <= T(0)) acc[p].v[i] = T(0);
+                }
+            }
+        }
+    }
     T divisor = T(1);
     const bool divide = a.div_counts != nullptr;
     if (divide) divisor = (T)max(a.div_counts[row], 1);
@@ -151,46 +226,63 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kern
         acc[p] = vec_zero<T, VW>();
     }
 
-    // ---- row slots of this unit -------------------------------------------------------
     constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR;
     const int64_t direct_units = (a.n_direct + RPU - 1) / RPU;
-    int my_row = 0, s0 = 0, d0 = 0, s1 = 0, d1 = 0;
-    bool my_write = false;
-    int nr;
-    int64_t item_index = -1;
-    int4 lr = make_int4(0, 0, 0, 0);
-    int long_index = 0;
-    if (unit < direct_units) {
-        const int64_t first = unit * RPU;
-        nr = (int)min((int64_t)RPU, a.n_direct - first);
-        if (gl < nr) {
-            my_row = a.row_ids ? a.row_ids[first + gl] : (int32_t)(first + gl);
-            s0 = a.rowptr[0][my_row];
-            d0 = a.rowptr[0][my_row + 1] - s0;
-            if (a.nterms > 1) {
-                s1 = a.rowptr[1][my_row];
-                d1 = a.rowptr[1][my_row + 1] - s1;
-            }
-            my_write = d0 + d1 <= a.split;  // longer rows are served by chunk units
-            if (!my_write) d0 = d1 = 0;
-        }
-    } else {
-        item_index = unit - direct_units;
+
+    if (unit >= direct_units) {
+        // ---- chunk of a long row: sum it, publish the partial sum, last ticket adds them up
+        const int64_t item_index = unit - direct_units;
         if (item_index >= a.n_items) return;
         const int4 item = a.items[item_index];
-        long_index = item.x;
-        lr = a.longs[item.x];
-        nr = 1;
-        if (gl == 0) {
-            my_row = lr.x;
-            if (item.y == 0) {
-                s0 = item.z;
-                d0 = item.w - item.z;
-            } else {
-                s1 = item.z;
-                d1 = item.w - item.z;
+        const int4 lr = a.longs[item.x];
+        const int t = item.y;
+        gather_range<T, VW, LPR, VPL, U, MASKED>(acc, a.col[t], a.val[t], a.src[t], a.mask_src,
+                                                 width, colbase, colok, item.z, item.w, gl, gmask);
+        T *part = a.partial + item_index * width + colbase;
+#pragma unroll
+        for (int p = 0; p < VPL; ++p)
+            if (colok[p]) vec_store<T, VW>(part + p * (LPR * VW), acc[p]);
+        __threadfence();
+        __syncwarp(gmask);
+        int *tk = a.tickets + (int64_t)item.x * gridDim.y + blockIdx.y;
+        int ticket = 0;
+        if (gl == 0) ticket = atomicAdd(tk, 1);
+        ticket = __shfl_sync(gmask, ticket, 0, LPR);
+        if (ticket != lr.z - 1) return;
+        __threadfence();
+#pragma unroll
+        for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
+        for (int s = 0; s < lr.z; ++s) {
+            const T *ps = a.partial + (int64_t)(lr.y + s) * width + colbase;
+#pragma unroll
+            for (int p = 0; p < VPL; ++p) {
+                if (colok[p]) {
+                    const V q = vec_load_cg<T, VW>(ps + p * (LPR * VW));
+#pragma unroll
+                    for (int i = 0; i < VW; ++i) acc[p].v[i] += q.v[i];
+                }
             }
         }
+        if (gl == 0) *tk = 0;  // leave the ticket ready for the next launch
+        finish_row<T, VW, LPR, VPL>(a, lr.x, acc, colbase, colok);
+        return;
+    }
+
+    // ---- row slots of this unit: up to RPU rows of the direct row list --------------------
+    int my_row = 0, s0 = 0, d0 = 0, s1 = 0, d1 = 0;
+    bool my_write = false;
+    const int64_t first = unit * RPU;
+    const int nr = (int)min((int64_t)RPU, a.n_direct - first);
+    if (gl < nr) {
+        my_row = a.row_ids ? a.row_ids[first + gl] : (int32_t)(first + gl);
+        s0 = a.rowptr[0][my_row];
+        d0 = a.rowptr[0][my_row + 1] - s0;
+        if (a.nterms > 1) {
+            s1 = a.rowptr[1][my_row];
+            d1 = a.rowptr[1][my_row + 1] - s1;
+        }
+        my_write = d0 + d1 <= a.split;  // longer rows are served by chunk units
+        if (!my_write) d0 = d1 = 0;
     }
     // exclusive prefix of the slot lengths inside the group
     const int deg = d0 + d1;
@@ -252,17 +344,18 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kern
     for (int base = 0; base < total; base += LPR) {
         if (base + LPR < total) fetch(base + LPR + gl, c_next, v_next, qt_next);
         const int cnt = min(LPR, total - base);
+        // bit j: entry j of this batch starts a new row slot (bit 0 always set: compare with cur)
+        const int prev_slot = __shfl_up_sync(gmask, qt, 1, LPR) & 0xff;
+        const unsigned ballot = __ballot_sync(gmask, gl == 0 || (qt & 0xff) != prev_slot);
+        const unsigned bmask = LPR == 32 ? ballot : ((ballot >> (lane & ~(LPR - 1))) & ((1u << LPR) - 1u));
         for (int j = 0; j < cnt; j += U) {
             V x[U][VPL];
-            T w[U];
-            int slot[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int cj = __shfl_sync(gmask, c, j + u, LPR);
-                w[u] = __shfl_sync(gmask, v, j + u, LPR);
-                slot[u] = __shfl_sync(gmask, qt, j + u, LPR);
+                const int term = __shfl_sync(gmask, qt, j + u, LPR) >> 8;
                 if (j + u < cnt) {
-                    const T *src = (slot[u] >> 8) ? a.src[1] : a.src[0];
+                    const T *src = term ? a.src[1] : a.src[0];
                     const int64_t off = (int64_t)cj * width + colbase;
 #pragma unroll
                     for (int p = 0; p < VPL; ++p) {
@@ -278,17 +371,37 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kern
                     }
                 }
             }
+            // Row boundaries inside this batch are rare for long rows and absent for chunks:
+            // test once per batch and keep the per-entry check out of the common path.
+            if (((bmask >> j) & ((1u << U) - 1u)) == 0u) {
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (j + u < cnt) {
-                    const int q = slot[u] & 0xff;
-                    if (q != cur) flush_until(q);
+                for (int u = 0; u < U; ++u) {
+                    const T w = __shfl_sync(gmask, v, j + u, LPR);
+                    if (j + u < cnt) {
 #pragma unroll
-                    for (int p = 0; p < VPL; ++p) {
-                        if (colok[p]) {
+                        for (int p = 0; p < VPL; ++p) {
+                            if (colok[p]) {
 #pragma unroll
-                            for (int i = 0; i < VW; ++i)
-                                acc[p].v[i] = fma(x[u][p].v[i], w[u], acc[p].v[i]);
+                                for (int i = 0; i < VW; ++i)
+                                    acc[p].v[i] = fma(x[u][p].v[i], w, acc[p].v[i]);
+                            }
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const T w = __shfl_sync(gmask, v, j + u, LPR);
+                    const int q = __shfl_sync(gmask, qt, j + u, LPR) & 0xff;
+                    if (j + u < cnt) {
+                        if (q != cur) flush_until(q);
+#pragma unroll
+                        for (int p = 0; p < VPL; ++p) {
+                            if (colok[p]) {
+#pragma unroll
+                                for (int i = 0; i < VW; ++i)
+                                    acc[p].v[i] = fma(x[u][p].v[i], w, acc[p].v[i]);
+                            }
                         }
                     }
                 }
@@ -299,39 +412,7 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kern
         qt = qt_next;
     }
 
-    if (item_index < 0) {
-        flush_until(nr);
-        return;
-    }
-
-    // ---- chunk of a long row: publish the partial sum, last ticket adds them up ---------
-    T *part = a.partial + item_index * width + colbase;
-#pragma unroll
-    for (int p = 0; p < VPL; ++p)
-        if (colok[p]) vec_store<T, VW>(part + p * (LPR * VW), acc[p]);
-    __threadfence();
-    __syncwarp(gmask);
-    int *tk = a.tickets + (int64_t)long_index * gridDim.y + blockIdx.y;
-    int ticket = 0;
-    if (gl == 0) ticket = atomicAdd(tk, 1);
-    ticket = __shfl_sync(gmask, ticket, 0, LPR);
-    if (ticket != lr.z - 1) return;
-    __threadfence();
-#pragma unroll
-    for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
-    for (int s = 0; s < lr.z; ++s) {
-        const T *ps = a.partial + (int64_t)(lr.y + s) * width + colbase;
-#pragma unroll
-        for (int p = 0; p < VPL; ++p) {
-            if (colok[p]) {
-                const V q = vec_load_cg<T, VW>(ps + p * (LPR * VW));
-#pragma unroll
-                for (int i = 0; i < VW; ++i) acc[p].v[i] += q.v[i];
-            }
-        }
-    }
-    if (gl == 0) *tk = 0;  // leave the ticket ready for the next launch
-    finish_row<T, VW, LPR, VPL>(a, lr.x, acc, colbase, colok);
+    flush_until(nr);
 }
 
 template <typename T, int VW, int LPR, int VPL, bool MASKED>
@@ -367,7 +448,8 @@ static int64_t ticket_tiles(int64_t width) { return std::max<int64_t>(1, ceil_di
 
 template <typename T>
 static int run_typed(const cgnn_plan *p, int64_t width, const T *val0, const T *src0,
-                     const T *val1, const T *src1, const T *mask, const int32_t *div_counts,
+                     const T *val1, const T *src1, const T *mask, const T *seg_mask,
+                     const int32_t *div_counts,
                      T *out, int accumulate, void *scratch, size_t scratch_bytes,
                      cudaStream_t stream) {
     constexpr int VWMAX = 16 / (int)sizeof(T);
@@ -381,6 +463,7 @@ static int run_typed(const cgnn_plan *p, int64_t width, const T *val0, const T *
     a.src[0] = src0; a.src[1] = src1;
     a.nterms = p->nterms;
     a.mask_src = mask;
+    a.seg_mask = seg_mask;
     a.div_counts = div_counts;
     a.out = out;
     a.accumulate = accumulate;
@@ -393,7 +476,7 @@ static int run_typed(const cgnn_plan *p, int64_t width, const T *val0, const T *
     a.longs = p->longs;
 
     const bool vec = width % VWMAX == 0 && aligned16(src0) && aligned16(src1) &&
-                     aligned16(mask) && aligned16(out);
+                     aligned16(mask) && aligned16(seg_mask) && aligned16(out);
     const size_t ticket_bytes =
         align_up((size_t)p->n_long * (size_t)ticket_tiles(width) * sizeof(int), 256);
     const size_t need = ticket_bytes + (size_t)p->n_items * (size_t)width * sizeof(T);
@@ -419,7 +502,7 @@ static int run_typed(const cgnn_plan *p, int64_t width, const T *val0, const T *
 }
 
 static int run(const cgnn_plan *p, int dtype, int64_t width, const void *val0, const void *src0,
-               const void *val1, const void *src1, const void *mask,
+               const void *val1, const void *src1, const void *mask, const void *seg_mask,
                const int32_t *div_counts, void *out, int accumulate, void *scratch,
                size_t scratch_bytes, cudaStream_t stream) {
     CGNN_REQUIRE(p != nullptr, "segment reduce: null plan");
@@ -434,11 +517,11 @@ static int run(const cgnn_plan *p, int dtype, int64_t width, const void *val0, c
     if (dtype == CGNN_F32)
         return run_typed<float>(p, width, (const float *)val0, (const float *)src0,
                                 (const float *)val1, (const float *)src1, (const float *)mask,
-                                div_counts, (float *)out, accumulate, scratch, scratch_bytes,
+                                (const float *)seg_mask, div_counts, (float *)out, accumulate, scratch, scratch_bytes,
                                 stream);
     return run_typed<double>(p, width, (const double *)val0, (const double *)src0,
                              (const double *)val1, (const double *)src1, (const double *)mask,
-                             div_counts, (double *)out, accumulate, scratch, scratch_bytes,
+                             (const double *)seg_mask, div_counts, (double *)out, accumulate, scratch, scratch_bytes,
                              stream);
 }
 
@@ -680,7 +763,7 @@ int cgnn_spmm(const cgnn_plan *plan, int dtype, int64_t width, const void *val, 
               void *out, int accumulate, void *scratch, size_t scratch_bytes,
               cgnn_stream_t stream) {
     CGNN_REQUIRE(plan != nullptr && plan->nterms == 1, "spmm: plan must hold one block");
-    return run(plan, dtype, width, val, src, nullptr, nullptr, nullptr, nullptr, out, accumulate,
+    return run(plan, dtype, width, val, src, nullptr, nullptr, nullptr, nullptr, nullptr, out, accumulate,
                scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
@@ -688,7 +771,7 @@ int cgnn_spmm_pair(const cgnn_plan *plan, int dtype, int64_t width, const void *
                    const void *src0, const void *val1, const void *src1, void *out,
                    int accumulate, void *scratch, size_t scratch_bytes, cgnn_stream_t stream) {
     CGNN_REQUIRE(plan != nullptr && plan->nterms == 2, "spmm_pair: plan must hold two blocks");
-    return run(plan, dtype, width, val0, src0, val1, src1, nullptr, nullptr, out, accumulate,
+    return run(plan, dtype, width, val0, src0, val1, src1, nullptr, nullptr, nullptr, out, accumulate,
                scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
@@ -697,7 +780,7 @@ int cgnn_cluster_mean(const cgnn_plan *plan, int dtype, int64_t width, const voi
                       cgnn_stream_t stream) {
     CGNN_REQUIRE(plan != nullptr && plan->nterms == 1, "cluster_mean: bad plan");
     CGNN_REQUIRE(count != nullptr, "cluster_mean: null counts");
-    return run(plan, dtype, width, nullptr, x, nullptr, nullptr, nullptr, count, out, 0, scratch,
+    return run(plan, dtype, width, nullptr, x, nullptr, nullptr, nullptr, nullptr, count, out, 0, scratch,
                scratch_bytes, (cudaStream_t)stream);
 }
 
@@ -706,10 +789,12 @@ int cgnn_cluster_reconstruct_backward(const cgnn_plan *plan, int dtype, int64_t 
                                       void *d_reps, void *bias_grad, void *scratch,
                                       size_t scratch_bytes, cgnn_stream_t stream) {
     CGNN_REQUIRE(plan != nullptr && plan->nterms == 1, "reconstruct_backward: bad plan");
+    CGNN_REQUIRE(relu >= 0 && relu <= 2, "reconstruct_backward: relu mode must be 0, 1 or 2");
     CGNN_REQUIRE(!relu || output != nullptr || plan->nnz[0] == 0,
                  "reconstruct_backward: relu needs the forward output");
-    int rc = run(plan, dtype, width, nullptr, grad, nullptr, nullptr, relu ? output : nullptr,
-                 nullptr, d_reps, 0, scratch, scratch_bytes, (cudaStream_t)stream);
+    int rc = run(plan, dtype, width, nullptr, grad, nullptr, nullptr, relu == 1 ? output : nullptr,
+                 relu == 2 ? output : nullptr, nullptr, d_reps, 0, scratch, scratch_bytes,
+                 (cudaStream_t)stream);
     if (rc != CGNN_OK || bias_grad == nullptr || width == 0) return rc;
     const size_t elt = dtype == CGNN_F64 ? 8 : 4;
     const size_t off = cgnn_plan_ticket_bytes(plan, width, dtype) +

@@ -26,8 +26,10 @@ class _Reconstruct(torch.autograd.Function):
     @once_differentiable
     def backward(ctx, grad):
         index, output = ctx.saved_tensors
+        # `output` is this Function's own forward result, so one mask row per group suffices.
         result = _native.cluster_reconstruct_backward(grad.contiguous(), index, output, ctx.groups,
-                                                      ctx.relu, return_bias_grad=ctx.has_bias)
+                                                      ctx.relu, return_bias_grad=ctx.has_bias,
+                                                      output_is_forward_result=True)
         if ctx.has_bias:
             return result[0], None, result[1], None
         return result, None, None, None

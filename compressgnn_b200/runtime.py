@@ -416,9 +416,10 @@ def cluster_mean_backward(grad, index, count):
     if out.numel() == 0:
         return out
     with torch.cuda.device(grad.device):
+        scaled = torch.empty_like(grad)  # grad / count, divided once per group row
         check(lib().cgnn_cluster_mean_backward(_dtype_code(grad), index.numel(), grad.size(1),
                                                grad.size(0), _ptr(grad), _ptr(index), _ptr(count),
-                                               _ptr(out), _stream_ptr(grad.device)))
+                                               _ptr(out), _ptr(scaled), _stream_ptr(grad.device)))
     return out
 
 
@@ -442,10 +443,13 @@ def cluster_reconstruct(reps, index, bias, relu):
 
 
 def cluster_reconstruct_backward(grad, index, output, groups, relu, plan=None,
-                                 return_bias_grad=False):
+                                 return_bias_grad=False, output_is_forward_result=False):
     """``d_reps[g] = sum over rows r with index[r] == g of (relu and output[r] <= 0 ? 0 :
     grad[r])``.  With ``return_bias_grad`` also returns the column sums of ``d_reps`` (the
-    bias gradient), computed in the same call."""
+    bias gradient), computed in the same call.  ``output_is_forward_result`` promises that
+    ``output`` is what ``cluster_reconstruct`` returned for this ``index`` (rows of a group are
+    then identical), which lets the kernel read one mask row per group instead of all of
+    ``output``."""
     _check_float(grad)
     _check_index(index, grad.device)
     _check_float(output)
@@ -467,7 +471,8 @@ def cluster_reconstruct_backward(grad, index, output, groups, relu, plan=None,
     sp, sb = plan.scratch(width, code)
     with torch.cuda.device(grad.device):
         check(lib().cgnn_cluster_reconstruct_backward(
-            plan.handle, code, width, _ptr(grad), _ptr(output), 1 if relu else 0, _ptr(out),
+            plan.handle, code, width, _ptr(grad), _ptr(output),
+            (2 if output_is_forward_result else 1) if relu else 0, _ptr(out),
             _ptr(bias_grad) if return_bias_grad else None, sp, sb, _stream_ptr(grad.device)))
     return (out, bias_grad) if return_bias_grad else out
 

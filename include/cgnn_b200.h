@@ -144,10 +144,13 @@ int cgnn_cluster_mean(const cgnn_plan *plan, int dtype, int64_t width, const voi
                       cgnn_stream_t stream);
 
 /* out[r,:] = grad[index[r],:] / max(count[index[r]],1)
- * ref: cluster_mean_backward_cuda, cluster_kernel.cu:171-181. */
+ * ref: cluster_mean_backward_cuda, cluster_kernel.cu:171-181.
+ * `scaled` is optional scratch of groups*width elements: when given, the division is done
+ * once per group row into it and the node rows are a pure gather (same bits, far fewer
+ * divisions); when NULL every output element is divided on the fly. */
 int cgnn_cluster_mean_backward(int dtype, int64_t n, int64_t width, int64_t groups,
                                const void *grad, const int64_t *index, const int32_t *count,
-                               void *out, cgnn_stream_t stream);
+                               void *out, void *scaled, cgnn_stream_t stream);
 
 /* out[r,:] = act(reps[index[r],:] + bias[:]); bias may be NULL; relu: v < 0 ? 0 : v.
  * ref: cluster_reconstruct_cuda, cluster_kernel.cu:182-195. */
@@ -156,6 +159,10 @@ int cgnn_cluster_reconstruct(int dtype, int64_t n, int64_t width, int64_t groups
                              int relu, void *out, cgnn_stream_t stream);
 
 /* d_reps[g,:] = sum_{index[r]==g} (relu && output[r,:] <= 0 ? 0 : grad[r,:]);
+ * relu: 0 = no mask; 1 = mask read per node row from `output` (the reference's semantics for
+ * any `output`); 2 = `output` is known to be the forward result of cgnn_cluster_reconstruct,
+ * whose rows are identical inside a group, so one output row per group is read and the
+ * group sum is masked once -- half the memory traffic, same result.
  * bias_grad (optional, [width]) = column sums of d_reps, the value the reference derives
  * in Python (ref: layer/CompressgnnReconstruct.py:26).
  * ref: cluster_reconstruct_backward_cuda, cluster_kernel.cu:196-208 (float atomics there). */

@@ -112,6 +112,16 @@ def test_large_mean_is_deterministic_with_long_segments(rt):
     np.testing.assert_array_equal(ids.cpu().numpy(), rids)
     plan = rt.index_plan(ids, active + 1)
     assert plan.long_rows > 0
+    reps = rng.standard_normal((active + 1, 64)).astype(np.float32)
+    bias = rng.standard_normal(64).astype(np.float32)
+    fwd = rt.cluster_reconstruct(cu(reps), ids, cu(bias), True)
+    go = cu(rng.standard_normal((n, 64)).astype(np.float32))
+    exact = rt.cluster_reconstruct_backward(go, ids, fwd, active + 1, True)
+    fast = rt.cluster_reconstruct_backward(go, ids, fwd, active + 1, True, output_is_forward_result=True)
+    assert torch.equal(exact, fast)
+    assert_close_rel(exact.cpu().numpy(),
+                     oracle.reconstruct_backward(go.cpu().numpy(), rids, fwd.cpu().numpy(), active + 1, True)[0],
+                     what="long reconstruct backward")
     y1 = rt.cluster_mean(dx, ids, counts)
     y2 = rt.cluster_mean(dx, ids, counts)
     assert torch.equal(y1, y2)
@@ -158,6 +168,9 @@ def test_reconstruct_grid(rt, dtype, width, relu):
     assert_close_rel(dr.cpu().numpy(), rdr, what="d_reps")
     assert_close_rel(db.cpu().numpy(), rdb, what="d_bias")
     assert not dr[0].any() and not dr[2].any() and not dr[4].any()
+    # one mask row per group instead of the whole forward output: same bits
+    dr2 = rt.cluster_reconstruct_backward(cu(go), cu(idx), y, 5, relu, output_is_forward_result=True)
+    assert torch.equal(dr, dr2)
 
 
 def test_argument_errors_raise_runtime_error(rt):
