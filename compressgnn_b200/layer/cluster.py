@@ -54,9 +54,8 @@ def _assign(input, planes, bits, workspace=None, process_group=None):
             workspace = _native.cluster_workspace(input, bits)
         if process_group is None:
             return _native.cluster_assign(input, planes, bits, workspace)
-        import torch.distributed as dist
-        partial = _native.project(input, planes)
-        dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=process_group)
+        from ..dist import allreduce_projection
+        partial = allreduce_projection(_native.project(input, planes), process_group)
         return _native.cluster_assign_from_projection(partial, workspace)
 
 
