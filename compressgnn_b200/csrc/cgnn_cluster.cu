@@ -466,17 +466,13 @@ int cgnn_cluster_assign_export(const void *workspace, int64_t n, int64_t active,
     CGNN_LAUNCH_CHECK();
     if (!plan_out) return CGNN_OK;
     cgnn_plan *p = new cgnn_plan();
-    CGNN_CUDA(cudaGetDevice(&p->device));
+    cudaGetDevice(&p->device);
     p->rows = active + 1;
     p->nterms = 1;
     p->nnz[0] = n;
-    CGNN_CUDA(cudaMalloc(&p->rowptr[0], sizeof(int32_t) * (size_t)(active + 2)));
-    CGNN_CUDA(cudaMalloc(&p->col[0], sizeof(int32_t) * (size_t)n));
-    CGNN_CUDA(cudaMemcpyAsync(p->rowptr[0], L.segstart, sizeof(int32_t) * (size_t)(active + 2),
-                              cudaMemcpyDeviceToDevice, stream));
-    CGNN_CUDA(cudaMemcpyAsync(p->col[0], L.vals[0], sizeof(int32_t) * (size_t)n,
-                              cudaMemcpyDeviceToDevice, stream));
-    int rc = plan_analyze(p, split, stream);
+    const int32_t *rp[2] = {L.segstart, nullptr};
+    const int32_t *cl[2] = {L.vals[0], nullptr};
+    int rc = plan_build(p, rp, cl, split, stream);
     if (rc != CGNN_OK) {
         cgnn_plan_destroy(p);
         return rc;
@@ -495,19 +491,18 @@ int cgnn_plan_create_from_index(cgnn_plan **plan_out, const int64_t *index, int6
     CGNN_REQUIRE(index != nullptr || n == 0, "plan_from_index: null index");
     CGNN_REQUIRE(groups > 0 || n == 0, "plan_from_index: entries but no groups");
     cgnn_plan *p = new cgnn_plan();
-    CGNN_CUDA(cudaGetDevice(&p->device));
+    cudaGetDevice(&p->device);
     p->rows = groups;
     p->nterms = 1;
     p->nnz[0] = n;
-    CGNN_CUDA(cudaMalloc(&p->rowptr[0], sizeof(int32_t) * (size_t)(groups + 1)));
-    CGNN_CUDA(cudaMalloc(&p->col[0], sizeof(int32_t) * (size_t)std::max<int64_t>(n, 1)));
     void *ws = nullptr;
-    int32_t *hist = nullptr;
+    int32_t *hist = nullptr, *rowptr = nullptr;
     int rc = CGNN_OK;
     do {
         AssignLayout L0 = assign_layout(nullptr, n);
         if (cudaMalloc(&ws, L0.total) != cudaSuccess ||
-            cudaMalloc(&hist, sizeof(int32_t) * (size_t)(groups + 1)) != cudaSuccess) {
+            cudaMalloc(&hist, sizeof(int32_t) * (size_t)(groups + 1)) != cudaSuccess ||
+            cudaMalloc(&rowptr, sizeof(int32_t) * (size_t)(groups + 1)) != cudaSuccess) {
             set_error("plan_from_index: device allocation failed");
             rc = CGNN_ERR_CUDA;
             break;
@@ -521,16 +516,13 @@ int cgnn_plan_create_from_index(cgnn_plan **plan_out, const int64_t *index, int6
             int32_t *sorted = nullptr;
             rc = sort_pairs(L, n, bits, &sorted, stream);
             if (rc != CGNN_OK) break;
-            cudaMemcpyAsync(p->col[0], L.vals[0], sizeof(int32_t) * (size_t)n,
-                            cudaMemcpyDeviceToDevice, stream);
         }
         size_t bytes = L.temp_bytes;
-        // The scan temp was sized for max(n,1)+2 items; a histogram longer than that gets
-        // its own temp.
+        // The scan temp was sized for max(n,1)+2 items; a longer histogram gets its own.
         void *temp = L.temp;
         void *own_temp = nullptr;
         size_t need = 0;
-        cub::DeviceScan::ExclusiveSum(nullptr, need, hist, p->rowptr[0], (int)(groups + 1));
+        cub::DeviceScan::ExclusiveSum(nullptr, need, hist, rowptr, (int)(groups + 1));
         if (need > bytes) {
             if (cudaMalloc(&own_temp, need) != cudaSuccess) {
                 set_error("plan_from_index: device allocation failed");
@@ -540,8 +532,7 @@ int cgnn_plan_create_from_index(cgnn_plan **plan_out, const int64_t *index, int6
             temp = own_temp;
             bytes = need;
         }
-        cudaError_t e = cub::DeviceScan::ExclusiveSum(temp, bytes, hist, p->rowptr[0],
-                                                      (int)(groups + 1), stream);
+        cudaError_t e = cub::DeviceScan::ExclusiveSum(temp, bytes, hist, rowptr, (int)(groups + 1), stream);
         cudaStreamSynchronize(stream);
         if (own_temp) cudaFree(own_temp);
         if (e != cudaSuccess) {
@@ -557,10 +548,13 @@ int cgnn_plan_create_from_index(cgnn_plan **plan_out, const int64_t *index, int6
             rc = CGNN_ERR_INVALID;
             break;
         }
-        rc = plan_analyze(p, split, stream);
+        const int32_t *rp[2] = {rowptr, nullptr};
+        const int32_t *cl[2] = {L.vals[0], nullptr};
+        rc = plan_build(p, rp, cl, split, stream);
     } while (0);
     if (ws) cudaFree(ws);
     if (hist) cudaFree(hist);
+    if (rowptr) cudaFree(rowptr);
     if (rc != CGNN_OK) {
         cgnn_plan_destroy(p);
         return rc;

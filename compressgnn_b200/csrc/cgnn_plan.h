@@ -3,29 +3,42 @@
 #pragma once
 #include "cgnn_common.cuh"
 
+// A plan owns a re-laid-out copy of the block's (or the two fused blocks') entries:
+//   entries[0 .. direct_entries)        the entries of the short rows, row after row in the
+//                                       order of the direct row list (a row's term-0 entries
+//                                       first, then its term-1 entries);
+//   entries[direct_entries .. total)    the entries of the long rows, cut into chunks.
+// An entry is the 32-bit source row with the term in bit 31.  `vperm` records where each entry
+// came from (index into the concatenation of the callers' two value arrays) so that values
+// can be brought into the same order once.
 struct cgnn_plan {
     int device = 0;
     int nterms = 1;
     int64_t rows = 0;
     int64_t nnz[2] = {0, 0};
-    int32_t *rowptr[2] = {nullptr, nullptr};  // device int32[rows+1], owned
-    int32_t *col[2] = {nullptr, nullptr};     // device int32[nnz], owned
-    int split = 0;                            // longest row a single lane group owns
-    int64_t n_long = 0;                       // rows longer than split
-    int64_t n_items = 0;                      // chunks of long rows (one partial-sum slot each)
-    int64_t n_direct = 0;                     // work units that are whole rows
-    int4 *items = nullptr;                    // device {long row index, term, e0, e1}
-    int4 *longs = nullptr;                    // device {row, first item, items, 0}
-    int32_t *row_ids = nullptr;               // device compact list of short non-empty rows, or null
+    int64_t total = 0;             // nnz[0] + nnz[1]
+    int32_t *entries = nullptr;    // device int32[total]
+    int32_t *vperm = nullptr;      // device int32[total]
+    int32_t *uptr = nullptr;       // device int32[n_direct + 1]: entry offset of each listed row
+    int32_t *urow = nullptr;       // device int32[n_direct]: row id of each listed row, or null = identity
+    int split = 0;                 // longest row kept in the direct list
+    int64_t n_direct = 0;          // rows in the direct list
+    int64_t n_long = 0;            // rows longer than split
+    int64_t n_items = 0;           // chunks of long rows (one partial-sum slot each)
+    int4 *items = nullptr;         // device {long row index, first entry, end entry, 0}
+    int4 *longs = nullptr;         // device {row, first item, items, first entry of the row}
+    int compact = 0;               // 1: empty rows are not listed (a fresh output is cleared first)
 };
 
 namespace cgnn {
 
-// Takes ownership of p->rowptr[t] / p->col[t] (device int32 arrays, already filled on
-// `stream`), reads the row pointers back, validates them and cuts the rows into work units.
-int plan_analyze(cgnn_plan *p, int split, cudaStream_t stream);
+// Build the plan's work lists and entry layout from device int32 CSR arrays of one or two
+// blocks over the same rows (p->rows, p->nterms, p->nnz set by the caller).  The inputs are
+// only read; synchronises `stream`.
+int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *const col[2], int split,
+               cudaStream_t stream);
 
-// Device status word of the segment-reduce translation unit (read-and-clear).
+// Device status word of each translation unit (read-and-clear).
 int segreduce_status(int *out);
 int gather_status(int *out);
 int cluster_status(int *out);

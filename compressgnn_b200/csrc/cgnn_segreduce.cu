@@ -2,13 +2,13 @@
 //
 // One kernel serves the compressed-propagation SpMM blocks, the fused two-block pass, the
 // per-bucket mean and the reconstruct backward.  Design points (B200, HBM-bound):
-//   * a group of LPR lanes owns up to LPR consecutive rows; every lane keeps VPL 16-byte
-//     vectors of the current row in registers, so one gathered feature row is LPR*VPL
-//     coalesced 128-bit loads;
-//   * the entries of the group's rows are read as one stream: LPR (col,val) pairs per
-//     coalesced load (the next batch is requested before the current one is consumed),
-//     broadcast by shuffle; U gathered rows are in flight per lane before the FMAs issue,
-//     across row boundaries;
+//   * the plan stores the entries of the short rows back to back, so a group of LPR lanes
+//     that owns a few consecutive rows reads ONE contiguous entry range: LPR (source,value)
+//     pairs per coalesced load (the next batch is requested before the current one is
+//     consumed), broadcast by shuffle; U gathered feature rows are in flight per lane before
+//     the FMAs issue, across row boundaries, so a short row costs no pipeline restart;
+//   * every lane keeps VPL 16-byte vectors of the current row in registers, so one gathered
+//     feature row is LPR*VPL coalesced 128-bit loads;
 //   * rows longer than `split` are cut into chunks (work units of their own); a chunk
 //     writes its partial sum to scratch, takes a ticket, and the chunk that draws the last
 //     ticket adds the partials in chunk order -- deterministic, no float atomics, and no
@@ -28,14 +28,14 @@
 #ifndef CGNN_SEG_RPU
 #define CGNN_SEG_RPU 8      // rows per direct work unit (capped by the lane-group width)
 #endif
-#ifndef CGNN_SEG_STREAMHINT
-#define CGNN_SEG_STREAMHINT 0  // 1: evict-first loads of indices and streaming stores of rows
+#ifndef CGNN_SEG_PREFETCH
+#define CGNN_SEG_PREFETCH 1    // request the next (source,value) batch before consuming the current
 #endif
 #ifndef CGNN_SEG_THREADS
 #define CGNN_SEG_THREADS 128
 #endif
 #ifndef CGNN_SEG_MINBLOCKS
-#define CGNN_SEG_MINBLOCKS 5
+#define CGNN_SEG_MINBLOCKS 6
 #endif
 
 namespace cgnn {
@@ -73,11 +73,11 @@ int segreduce_status(int *out) {
 
 template <typename T>
 struct SegArgs {
-    const int32_t *rowptr[2];
-    const int32_t *col[2];
-    const T *val[2];
-    const T *src[2];
-    int nterms;
+    const int32_t *entries;     // source row | term << 31, in plan order
+    const T *val;               // values in plan order, or null (all ones)
+    const T *src0;              // source matrix of block 0
+    int32_t delta_rows;         // (source matrix of block 1) - src0 in whole rows, when aligned
+    int64_t delta_elems;        // the same distance in elements (GENERIC kernels)
     const T *mask_src;          // MASKED: entries whose mask_src value is <= 0 contribute 0
     const T *seg_mask;          // optional: the finished row is zeroed where the mask row of its
                                 // FIRST entry is <= 0 (all entries of a row share one mask row)
@@ -85,9 +85,9 @@ struct SegArgs {
     T *out;
     int accumulate;
     int64_t width;
-    const int32_t *row_ids;
+    const int32_t *uptr;
+    const int32_t *urow;
     int64_t n_direct;
-    int split;
     const int4 *items;
     int64_t n_items;
     const int4 *longs;
@@ -95,57 +95,42 @@ struct SegArgs {
     int *tickets;
 };
 
-// Sum of one contiguous entry range [e0, e1) of one block into acc: LPR (col,val) pairs per
-// coalesced load, U gathered rows in flight per lane.  Used for the chunks of long rows.
-template <typename T, int VW, int LPR, int VPL, int U, bool MASKED>
-__device__ __forceinline__ void gather_range(Vec<T, VW> (&acc)[VPL], const int32_t *col,
-                                             const T *val, const T *src, const T *mask,
-                                             int64_t width, int64_t colbase,
-                                             const bool (&colok)[VPL], int e0, int e1, int gl,
-                                             unsigned gmask) {
+// Source-row index of an entry relative to src0.  Entries of the second block (bit 31 set)
+// live in another matrix; when that matrix starts a whole number of rows away from src0
+// (delta_rows), adding it here -- once, in the lane that loaded the entry -- lets every
+// gather use the plain address row * width + column.  (Any per-gather select or extra 64-bit
+// term in that address costs about a third of the kernel's throughput on B200.)
+template <typename T>
+__device__ __forceinline__ int32_t entry_row(const SegArgs<T> &a, int32_t c) {
+    return (c & 0x7fffffff) + ((c >> 31) & a.delta_rows);
+}
+
+// Load U gathered feature rows (entries j .. j+U of the current batch) into registers.
+// GENERIC: the second matrix is not row-aligned with the first; its entries (flag kept in
+// bit 31 of r) add an element remainder.
+template <typename T, int VW, int LPR, int VPL, int U, bool MASKED, bool GENERIC>
+__device__ __forceinline__ void load_batch(const SegArgs<T> &a, Vec<T, VW> (&x)[U][VPL], int32_t r, int j,
+                                           int cnt, int64_t colbase, const bool (&colok)[VPL],
+                                           unsigned gmask) {
     using V = Vec<T, VW>;
-    for (int base = e0; base < e1; base += LPR) {
-        const int mine = base + gl;
-        int c = 0;
-        T v = T(0);
-        if (mine < e1) {
-            c = col[mine];
-            v = val ? val[mine] : T(1);
-        }
-        const int cnt = min(LPR, e1 - base);
-        for (int j = 0; j < cnt; j += U) {
-            V x[U][VPL];
-            T w[U];
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int cj = __shfl_sync(gmask, c, j + u, LPR);
-                w[u] = __shfl_sync(gmask, v, j + u, LPR);
-                if (j + u < cnt) {
-                    const int64_t off = (int64_t)cj * width + colbase;
+    for (int u = 0; u < U; ++u) {
+        const int32_t rj = __shfl_sync(gmask, r, j + u, LPR);
+        if (j + u < cnt) {
+            int64_t off;
+            if constexpr (GENERIC)
+                off = (int64_t)(rj & 0x7fffffff) * a.width + colbase + (rj < 0 ? a.delta_elems : (int64_t)0);
+            else
+                off = (int64_t)rj * a.width + colbase;
 #pragma unroll
-                    for (int p = 0; p < VPL; ++p) {
-                        if (colok[p]) {
-                            x[u][p] = gather_load<T, VW>(src + off + p * (LPR * VW));
-                            if constexpr (MASKED) {
-                                const V m = vec_load<T, VW>(mask + off + p * (LPR * VW));
+            for (int p = 0; p < VPL; ++p) {
+                if (colok[p]) {
+                    x[u][p] = gather_load<T, VW>(a.src0 + off + p * (LPR * VW));
+                    if constexpr (MASKED) {
+                        const V m = vec_load<T, VW>(a.mask_src + off + p * (LPR * VW));
 #pragma unroll
-                                for (int i = 0; i < VW; ++i)
-                                    if (m.v[i] <= T(0)) x[u][p].v[i] = T(0);
-                            }
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                if (j + u < cnt) {
-#pragma unroll
-                    for (int p = 0; p < VPL; ++p) {
-                        if (colok[p]) {
-#pragma unroll
-                            for (int i = 0; i < VW; ++i)
-                                acc[p].v[i] = fma(x[u][p].v[i], w[u], acc[p].v[i]);
-                        }
+                        for (int i = 0; i < VW; ++i)
+                            if (m.v[i] <= T(0)) x[u][p].v[i] = T(0);
                     }
                 }
             }
@@ -153,24 +138,35 @@ __device__ __forceinline__ void gather_range(Vec<T, VW> (&acc)[VPL], const int32
     }
 }
 
-// Store (or accumulate, or divide) one finished row.
+template <typename T, int VW, int VPL>
+__device__ __forceinline__ void fma_row(Vec<T, VW> (&acc)[VPL], const Vec<T, VW> (&x)[VPL], T w,
+                                        const bool (&colok)[VPL]) {
+#pragma unroll
+    for (int p = 0; p < VPL; ++p) {
+        if (colok[p]) {
+#pragma unroll
+            for (int i = 0; i < VW; ++i) acc[p].v[i] = fma(x[p].v[i], w, acc[p].v[i]);
+        }
+    }
+}
+
+// Store (or accumulate, or divide) one finished row; first_entry < 0 means the row is empty.
 template <typename T, int VW, int LPR, int VPL>
-__device__ __forceinline__ void finish_row(const SegArgs<T> &a, int32_t row, Vec<T, VW> (&acc)[VPL],
-                                           int64_t colbase, const bool (&colok)[VPL]) {
+__device__ __forceinline__ void finish_row(const SegArgs<T> &a, int32_t row, int first_entry,
+                                           Vec<T, VW> (&acc)[VPL], int64_t colbase,
+                                           const bool (&colok)[VPL]) {
     using V = Vec<T, VW>;
+    if (first_entry < 0 && a.accumulate) return;  // nothing to add
     T *orow = a.out + (int64_t)row * a.width + colbase;
-    if (a.seg_mask) {
-        const int first = a.rowptr[0][row];
-        if (first < a.rowptr[0][row + 1]) {
-            const T *mrow = a.seg_mask + (int64_t)a.col[0][first] * a.width + colbase;
+    if (a.seg_mask && first_entry >= 0) {
+        const T *mrow = a.seg_mask + (int64_t)(a.entries[first_entry] & 0x7fffffff) * a.width + colbase;
 #pragma unroll
-            for (int p = 0; p < VPL; ++p) {
-                if (colok[p]) {
-                    const V m = vec_load<T, VW>(mrow + p * (LPR * VW));
+        for (int p = 0; p < VPL; ++p) {
+            if (colok[p]) {
+                const V m = vec_load<T, VW>(mrow + p * (LPR * VW));
 #pragma unroll
-                    for (int i = 0; i < VW; ++i)
-                        if (m.v[i] <= T(0)) acc[p].v[i] = T(0);
-                }
+                for (int i = 0; i < VW; ++i)
+                    if (m.v[i] <= T(0)) acc[p].v[i] = T(0);
             }
         }
     }
@@ -190,26 +186,20 @@ __device__ __forceinline__ void finish_row(const SegArgs<T> &a, int32_t row, Vec
 #pragma unroll
                 for (int i = 0; i < VW; ++i) r.v[i] = r.v[i] / divisor;
             }
-#if CGNN_SEG_STREAMHINT
-            vec_store_cs<T, VW>(orow + p * (LPR * VW), r);
-#else
             vec_store<T, VW>(orow + p * (LPR * VW), r);
-#endif
         }
     }
 }
 
-// One work unit per group of LPR lanes: either up to LPR rows of the direct row list (their
-// entries are streamed as ONE sequence, so the loads of a row's gathered feature rows are in
-// flight together with its neighbours' and a short row costs no pipeline restart), or one
-// chunk of a long row.  Lane q of the group keeps the extent of row slot q; an entry's slot is
-// found by a shuffle binary search over the slots' prefix sums.
-template <typename T, int VW, int LPR, int VPL, bool MASKED>
+// One work unit per group of LPR lanes: a few consecutive rows of the direct list (one
+// contiguous entry range), or one chunk of a long row.
+template <typename T, int VW, int LPR, int VPL, bool MASKED, bool GENERIC>
 __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kernel(const SegArgs<T> a) {
     using V = Vec<T, VW>;
     constexpr int GPW = 32 / LPR;
     constexpr int U0 = VPL >= CGNN_SEG_USCALE ? 1 : CGNN_SEG_USCALE / VPL;
     constexpr int U = U0 < LPR ? U0 : LPR;
+    constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR - 1;
     const int lane = threadIdx.x & 31;
     const int gl = lane & (LPR - 1);
     const unsigned gmask =
@@ -225,219 +215,144 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kern
         colok[p] = colbase + p * (LPR * VW) < width;
         acc[p] = vec_zero<T, VW>();
     }
-
-    constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR;
     const int64_t direct_units = (a.n_direct + RPU - 1) / RPU;
 
-    if (unit >= direct_units) {
-        // ---- chunk of a long row: sum it, publish the partial sum, last ticket adds them up
-        const int64_t item_index = unit - direct_units;
+    int e_begin, e_end, nr = 0, myptr = 0;
+    int64_t first = 0;
+    int64_t item_index = -1;
+    if (unit < direct_units) {
+        first = unit * RPU;
+        nr = (int)min((int64_t)RPU, a.n_direct - first);
+        if (gl <= nr) myptr = a.uptr[first + gl];
+        e_begin = __shfl_sync(gmask, myptr, 0, LPR);
+        e_end = __shfl_sync(gmask, myptr, nr, LPR);
+    } else {
+        item_index = unit - direct_units;
         if (item_index >= a.n_items) return;
         const int4 item = a.items[item_index];
-        const int4 lr = a.longs[item.x];
-        const int t = item.y;
-        gather_range<T, VW, LPR, VPL, U, MASKED>(acc, a.col[t], a.val[t], a.src[t], a.mask_src,
-                                                 width, colbase, colok, item.z, item.w, gl, gmask);
-        T *part = a.partial + item_index * width + colbase;
-#pragma unroll
-        for (int p = 0; p < VPL; ++p)
-            if (colok[p]) vec_store<T, VW>(part + p * (LPR * VW), acc[p]);
-        __threadfence();
-        __syncwarp(gmask);
-        int *tk = a.tickets + (int64_t)item.x * gridDim.y + blockIdx.y;
-        int ticket = 0;
-        if (gl == 0) ticket = atomicAdd(tk, 1);
-        ticket = __shfl_sync(gmask, ticket, 0, LPR);
-        if (ticket != lr.z - 1) return;
-        __threadfence();
+        e_begin = item.y;
+        e_end = item.z;
+    }
+
+    // ---- stream the entry range -------------------------------------------------------
+    int cur = 0;              // listed row whose sum is in acc (direct units)
+    int row_begin = e_begin;  // its entry range
+    int row_end = item_index >= 0 ? e_end : __shfl_sync(gmask, myptr, 1, LPR);
+    auto flush = [&]() {  // finish listed row `cur` and move to the next one
+        const int32_t row = a.urow ? a.urow[first + cur] : (int32_t)(first + cur);
+        finish_row<T, VW, LPR, VPL>(a, row, row_begin < row_end ? row_begin : -1, acc, colbase, colok);
 #pragma unroll
         for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
-        for (int s = 0; s < lr.z; ++s) {
-            const T *ps = a.partial + (int64_t)(lr.y + s) * width + colbase;
-#pragma unroll
-            for (int p = 0; p < VPL; ++p) {
-                if (colok[p]) {
-                    const V q = vec_load_cg<T, VW>(ps + p * (LPR * VW));
-#pragma unroll
-                    for (int i = 0; i < VW; ++i) acc[p].v[i] += q.v[i];
-                }
-            }
-        }
-        if (gl == 0) *tk = 0;  // leave the ticket ready for the next launch
-        finish_row<T, VW, LPR, VPL>(a, lr.x, acc, colbase, colok);
-        return;
+        ++cur;
+        row_begin = row_end;
+        row_end = __shfl_sync(gmask, myptr, (cur + 1) & (LPR - 1), LPR);
+    };
+    auto row_of = [&](int32_t c) { return GENERIC ? c : entry_row(a, c); };
+    int32_t o = 0, o_next = 0;  // source row of this lane's entry of the batch
+    T v = T(0), v_next = T(0);
+    if (e_begin + gl < e_end) {
+        o = row_of(a.entries[e_begin + gl]);
+        v = a.val ? a.val[e_begin + gl] : T(1);
     }
-
-    // ---- row slots of this unit: up to RPU rows of the direct row list --------------------
-    int my_row = 0, s0 = 0, d0 = 0, s1 = 0, d1 = 0;
-    bool my_write = false;
-    const int64_t first = unit * RPU;
-    const int nr = (int)min((int64_t)RPU, a.n_direct - first);
-    if (gl < nr) {
-        my_row = a.row_ids ? a.row_ids[first + gl] : (int32_t)(first + gl);
-        s0 = a.rowptr[0][my_row];
-        d0 = a.rowptr[0][my_row + 1] - s0;
-        if (a.nterms > 1) {
-            s1 = a.rowptr[1][my_row];
-            d1 = a.rowptr[1][my_row + 1] - s1;
+    for (int base = e_begin; base < e_end; base += LPR) {
+#if CGNN_SEG_PREFETCH
+        const int nxt = base + LPR + gl;
+        if (nxt < e_end) {
+            o_next = row_of(a.entries[nxt]);
+            v_next = a.val ? a.val[nxt] : T(1);
         }
-        my_write = d0 + d1 <= a.split;  // longer rows are served by chunk units
-        if (!my_write) d0 = d1 = 0;
-    }
-    // exclusive prefix of the slot lengths inside the group
-    const int deg = d0 + d1;
-    int incl = deg;
-#pragma unroll
-    for (int o = 1; o < LPR; o <<= 1) {
-        const int t = __shfl_up_sync(gmask, incl, o, LPR);
-        if (gl >= o) incl += t;
-    }
-    const int P = incl - deg;
-    const int total = __shfl_sync(gmask, incl, LPR - 1, LPR);
-
-    // entry k of the unit's stream -> (column, value, slot | term << 8)
-    auto fetch = [&](int k, int &c, T &v, int &qt) {
-        int q = 0;
-#pragma unroll
-        for (int step = LPR / 2; step >= 1; step >>= 1) {
-            const int cand = q + step;
-            const int pc = __shfl_sync(gmask, P, cand & (LPR - 1), LPR);
-            if (cand < nr && pc <= k) q = cand;
-        }
-        const int pq = __shfl_sync(gmask, P, q, LPR);
-        const int s0q = __shfl_sync(gmask, s0, q, LPR);
-        const int d0q = __shfl_sync(gmask, d0, q, LPR);
-        const int s1q = __shfl_sync(gmask, s1, q, LPR);
-        c = 0;
-        v = T(0);
-        qt = q;
-        if (k < total) {
-            const int o = k - pq;
-            const int term = o >= d0q ? 1 : 0;
-            const int e = term ? s1q + (o - d0q) : s0q + o;
-            const T *vp = a.val[term];
-#if CGNN_SEG_STREAMHINT
-            c = __ldcs(a.col[term] + e);
-            v = vp ? __ldcs(vp + e) : T(1);
 #else
-            c = a.col[term][e];
-            v = vp ? vp[e] : T(1);
+        if (base != e_begin && base + gl < e_end) {
+            o = row_of(a.entries[base + gl]);
+            v = a.val ? a.val[base + gl] : T(1);
+        }
 #endif
-            qt = q | (term << 8);
-        }
-    };
-
-    int cur = 0;  // slot whose sum is in acc
-    auto flush_until = [&](int upto) {  // finish slots cur .. upto-1 (all but the first are empty)
-        for (; cur < upto; ++cur) {
-            const int row = __shfl_sync(gmask, my_row, cur, LPR);
-            const int wr = __shfl_sync(gmask, (int)my_write, cur, LPR);
-            if (wr) finish_row<T, VW, LPR, VPL>(a, row, acc, colbase, colok);
-#pragma unroll
-            for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
-        }
-    };
-
-    int c, qt, c_next = 0, qt_next = 0;
-    T v, v_next = T(0);
-    fetch(gl, c, v, qt);
-    for (int base = 0; base < total; base += LPR) {
-        if (base + LPR < total) fetch(base + LPR + gl, c_next, v_next, qt_next);
-        const int cnt = min(LPR, total - base);
-        // bit j: entry j of this batch starts a new row slot (bit 0 always set: compare with cur)
-        const int prev_slot = __shfl_up_sync(gmask, qt, 1, LPR) & 0xff;
-        const unsigned ballot = __ballot_sync(gmask, gl == 0 || (qt & 0xff) != prev_slot);
-        const unsigned bmask = LPR == 32 ? ballot : ((ballot >> (lane & ~(LPR - 1))) & ((1u << LPR) - 1u));
+        const int cnt = min(LPR, e_end - base);
         for (int j = 0; j < cnt; j += U) {
             V x[U][VPL];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int cj = __shfl_sync(gmask, c, j + u, LPR);
-                const int term = __shfl_sync(gmask, qt, j + u, LPR) >> 8;
-                if (j + u < cnt) {
-                    const T *src = term ? a.src[1] : a.src[0];
-                    const int64_t off = (int64_t)cj * width + colbase;
-#pragma unroll
-                    for (int p = 0; p < VPL; ++p) {
-                        if (colok[p]) {
-                            x[u][p] = gather_load<T, VW>(src + off + p * (LPR * VW));
-                            if constexpr (MASKED) {
-                                const V m = vec_load<T, VW>(a.mask_src + off + p * (LPR * VW));
-#pragma unroll
-                                for (int i = 0; i < VW; ++i)
-                                    if (m.v[i] <= T(0)) x[u][p].v[i] = T(0);
-                            }
-                        }
-                    }
-                }
-            }
-            // Row boundaries inside this batch are rare for long rows and absent for chunks:
-            // test once per batch and keep the per-entry check out of the common path.
-            if (((bmask >> j) & ((1u << U) - 1u)) == 0u) {
+            load_batch<T, VW, LPR, VPL, U, MASKED, GENERIC>(a, x, o, j, cnt, colbase, colok, gmask);
+            if (base + j + U <= row_end) {  // no row boundary inside this batch
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const T w = __shfl_sync(gmask, v, j + u, LPR);
-                    if (j + u < cnt) {
-#pragma unroll
-                        for (int p = 0; p < VPL; ++p) {
-                            if (colok[p]) {
-#pragma unroll
-                                for (int i = 0; i < VW; ++i)
-                                    acc[p].v[i] = fma(x[u][p].v[i], w, acc[p].v[i]);
-                            }
-                        }
-                    }
+                    if (j + u < cnt) fma_row<T, VW, VPL>(acc, x[u], w, colok);
                 }
             } else {
 #pragma unroll
                 for (int u = 0; u < U; ++u) {
                     const T w = __shfl_sync(gmask, v, j + u, LPR);
-                    const int q = __shfl_sync(gmask, qt, j + u, LPR) & 0xff;
                     if (j + u < cnt) {
-                        if (q != cur) flush_until(q);
-#pragma unroll
-                        for (int p = 0; p < VPL; ++p) {
-                            if (colok[p]) {
-#pragma unroll
-                                for (int i = 0; i < VW; ++i)
-                                    acc[p].v[i] = fma(x[u][p].v[i], w, acc[p].v[i]);
-                            }
-                        }
+                        while (base + j + u >= row_end) flush();
+                        fma_row<T, VW, VPL>(acc, x[u], w, colok);
                     }
                 }
             }
         }
-        c = c_next;
+#if CGNN_SEG_PREFETCH
+        o = o_next;
         v = v_next;
-        qt = qt_next;
+#endif
+    }
+    if (item_index < 0) {
+        while (cur < nr) flush();
+        return;
     }
 
-    flush_until(nr);
+    // ---- chunk of a long row: publish the partial sum, the last ticket adds them up --------
+    const int4 item = a.items[item_index];
+    const int4 lr = a.longs[item.x];
+    T *part = a.partial + item_index * width + colbase;
+#pragma unroll
+    for (int p = 0; p < VPL; ++p)
+        if (colok[p]) vec_store<T, VW>(part + p * (LPR * VW), acc[p]);
+    __threadfence();
+    __syncwarp(gmask);
+    int *tk = a.tickets + (int64_t)item.x * gridDim.y + blockIdx.y;
+    int ticket = 0;
+    if (gl == 0) ticket = atomicAdd(tk, 1);
+    ticket = __shfl_sync(gmask, ticket, 0, LPR);
+    if (ticket != lr.z - 1) return;
+    __threadfence();
+#pragma unroll
+    for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
+    for (int s = 0; s < lr.z; ++s) {
+        const T *ps = a.partial + (int64_t)(lr.y + s) * width + colbase;
+#pragma unroll
+        for (int p = 0; p < VPL; ++p) {
+            if (colok[p]) {
+                const V q = vec_load_cg<T, VW>(ps + p * (LPR * VW));
+#pragma unroll
+                for (int i = 0; i < VW; ++i) acc[p].v[i] += q.v[i];
+            }
+        }
+    }
+    if (gl == 0) *tk = 0;  // leave the ticket ready for the next launch
+    finish_row<T, VW, LPR, VPL>(a, lr.x, lr.w, acc, colbase, colok);
 }
 
-template <typename T, int VW, int LPR, int VPL, bool MASKED>
+template <typename T, int VW, int LPR, int VPL, bool MASKED, bool GENERIC>
 static int launch_cfg(const SegArgs<T> &a, cudaStream_t stream) {
-    constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR;
+    constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR - 1;
     const int64_t units = ceil_div(a.n_direct, RPU) + a.n_items;
     const int64_t per_block = (CGNN_SEG_THREADS / 32) * (32 / LPR);
     const int64_t gx = ceil_div(units, per_block);
     const int64_t gy = ceil_div(a.width, (int64_t)LPR * VPL * VW);
     CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
-    seg_kernel<T, VW, LPR, VPL, MASKED><<<dim3((unsigned)gx, (unsigned)gy), CGNN_SEG_THREADS, 0, stream>>>(a);
+    seg_kernel<T, VW, LPR, VPL, MASKED, GENERIC><<<dim3((unsigned)gx, (unsigned)gy), CGNN_SEG_THREADS, 0, stream>>>(a);
     CGNN_LAUNCH_CHECK();
     return CGNN_OK;
 }
 
-template <typename T, int VW, bool MASKED>
+template <typename T, int VW, bool MASKED, bool GENERIC>
 static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
     const int64_t vecs = a.width / VW;
-    if (vecs <= 4) return launch_cfg<T, VW, 4, 1, MASKED>(a, stream);
-    if (vecs <= 8) return launch_cfg<T, VW, 8, 1, MASKED>(a, stream);
-    if (vecs <= 16) return launch_cfg<T, VW, 16, 1, MASKED>(a, stream);
-    if (vecs <= 32) return launch_cfg<T, VW, 32, 1, MASKED>(a, stream);
-    if (vecs <= 64) return launch_cfg<T, VW, 32, 2, MASKED>(a, stream);
-    if (vecs <= 128) return launch_cfg<T, VW, 32, 4, MASKED>(a, stream);
-    return launch_cfg<T, VW, 32, 8, MASKED>(a, stream);
+    if (vecs <= 4) return launch_cfg<T, VW, 4, 1, MASKED, GENERIC>(a, stream);
+    if (vecs <= 8) return launch_cfg<T, VW, 8, 1, MASKED, GENERIC>(a, stream);
+    if (vecs <= 16) return launch_cfg<T, VW, 16, 1, MASKED, GENERIC>(a, stream);
+    if (vecs <= 32) return launch_cfg<T, VW, 32, 1, MASKED, GENERIC>(a, stream);
+    if (vecs <= 64) return launch_cfg<T, VW, 32, 2, MASKED, GENERIC>(a, stream);
+    if (vecs <= 128) return launch_cfg<T, VW, 32, 4, MASKED, GENERIC>(a, stream);
+    return launch_cfg<T, VW, 32, 8, MASKED, GENERIC>(a, stream);
 }
 
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -447,30 +362,28 @@ static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t
 static int64_t ticket_tiles(int64_t width) { return std::max<int64_t>(1, ceil_div(width, 256)); }
 
 template <typename T>
-static int run_typed(const cgnn_plan *p, int64_t width, const T *val0, const T *src0,
-                     const T *val1, const T *src1, const T *mask, const T *seg_mask,
-                     const int32_t *div_counts,
-                     T *out, int accumulate, void *scratch, size_t scratch_bytes,
-                     cudaStream_t stream) {
+static int run_typed(const cgnn_plan *p, int64_t width, const T *val, const T *src0, const T *src1,
+                     const T *mask, const T *seg_mask, const int32_t *div_counts, T *out,
+                     int accumulate, void *scratch, size_t scratch_bytes, cudaStream_t stream) {
     constexpr int VWMAX = 16 / (int)sizeof(T);
     if (p->rows == 0 || width == 0) return CGNN_OK;
     SegArgs<T> a;
-    for (int t = 0; t < 2; ++t) {
-        a.rowptr[t] = p->rowptr[t];
-        a.col[t] = p->col[t];
-    }
-    a.val[0] = val0; a.val[1] = val1;
-    a.src[0] = src0; a.src[1] = src1;
-    a.nterms = p->nterms;
+    a.entries = p->entries;
+    a.val = val;
+    a.src0 = src0 ? src0 : src1;
+    a.delta_elems = (src0 && src1) ? (int64_t)(src1 - src0) : 0;
+    const bool row_aligned = a.delta_elems % width == 0 && a.delta_elems / width > -0x7fffffffll &&
+                             a.delta_elems / width < 0x3fffffffll;
+    a.delta_rows = row_aligned ? (int32_t)(a.delta_elems / width) : 0;
     a.mask_src = mask;
     a.seg_mask = seg_mask;
     a.div_counts = div_counts;
     a.out = out;
     a.accumulate = accumulate;
     a.width = width;
-    a.row_ids = p->row_ids;
+    a.uptr = p->uptr;
+    a.urow = p->urow;
     a.n_direct = p->n_direct;
-    a.split = p->split;
     a.items = p->items;
     a.n_items = p->n_items;
     a.longs = p->longs;
@@ -490,19 +403,23 @@ static int run_typed(const cgnn_plan *p, int64_t width, const T *val0, const T *
     a.partial = reinterpret_cast<T *>(reinterpret_cast<char *>(scratch) + ticket_bytes);
 
     // A compact row list skips empty rows, so a fresh result has to be cleared first.
-    if (!accumulate && p->row_ids)
+    if (!accumulate && p->compact)
         CGNN_CUDA(cudaMemsetAsync(out, 0, (size_t)p->rows * (size_t)width * sizeof(T), stream));
     if (p->n_direct + p->n_items == 0) return CGNN_OK;
-    if (vec) {
-        if (mask) return launch_vw<T, VWMAX, true>(a, stream);
-        return launch_vw<T, VWMAX, false>(a, stream);
+    if (!row_aligned) {  // two sources that are not a whole number of rows apart
+        if (vec) return launch_vw<T, VWMAX, false, true>(a, stream);
+        return launch_vw<T, 1, false, true>(a, stream);
     }
-    if (mask) return launch_vw<T, 1, true>(a, stream);
-    return launch_vw<T, 1, false>(a, stream);
+    if (vec) {
+        if (mask) return launch_vw<T, VWMAX, true, false>(a, stream);
+        return launch_vw<T, VWMAX, false, false>(a, stream);
+    }
+    if (mask) return launch_vw<T, 1, true, false>(a, stream);
+    return launch_vw<T, 1, false, false>(a, stream);
 }
 
-static int run(const cgnn_plan *p, int dtype, int64_t width, const void *val0, const void *src0,
-               const void *val1, const void *src1, const void *mask, const void *seg_mask,
+static int run(const cgnn_plan *p, int dtype, int64_t width, const void *val, const void *src0,
+               const void *src1, const void *mask, const void *seg_mask,
                const int32_t *div_counts, void *out, int accumulate, void *scratch,
                size_t scratch_bytes, cudaStream_t stream) {
     CGNN_REQUIRE(p != nullptr, "segment reduce: null plan");
@@ -515,14 +432,12 @@ static int run(const cgnn_plan *p, int dtype, int64_t width, const void *val0, c
                      "segment reduce: null second source");
     }
     if (dtype == CGNN_F32)
-        return run_typed<float>(p, width, (const float *)val0, (const float *)src0,
-                                (const float *)val1, (const float *)src1, (const float *)mask,
-                                (const float *)seg_mask, div_counts, (float *)out, accumulate, scratch, scratch_bytes,
-                                stream);
-    return run_typed<double>(p, width, (const double *)val0, (const double *)src0,
-                             (const double *)val1, (const double *)src1, (const double *)mask,
-                             (const double *)seg_mask, div_counts, (double *)out, accumulate, scratch, scratch_bytes,
-                             stream);
+        return run_typed<float>(p, width, (const float *)val, (const float *)src0, (const float *)src1,
+                                (const float *)mask, (const float *)seg_mask, div_counts, (float *)out,
+                                accumulate, scratch, scratch_bytes, stream);
+    return run_typed<double>(p, width, (const double *)val, (const double *)src0, (const double *)src1,
+                             (const double *)mask, (const double *)seg_mask, div_counts, (double *)out,
+                             accumulate, scratch, scratch_bytes, stream);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -568,14 +483,55 @@ static int colsum(const T *x, int64_t rows, int64_t width, T *part, T *out, cuda
 }
 
 // ---------------------------------------------------------------------------------------
-// Plan analysis (host side, once per graph block or per assignment refresh).
+// Plan construction (once per graph block or per assignment refresh): the host cuts the rows
+// into work units from the row pointers alone; a kernel then copies the entries into the
+// plan's order.
 // ---------------------------------------------------------------------------------------
-int plan_analyze(cgnn_plan *p, int split, cudaStream_t stream) {
+__global__ void scatter_entries_kernel(const int32_t *rowptr, const int32_t *col, const int32_t *dst,
+                                       const int32_t *lead, int64_t rows, int term, int32_t value_base,
+                                       int32_t *entries, int32_t *vperm) {
+    // one warp per row; `lead` holds the row's term-0 length when this is term 1
+    const int lane = threadIdx.x & 31;
+    const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+        const int b = rowptr[r], e = rowptr[r + 1];
+        if (b == e) continue;
+        const int d = dst[r] + (lead ? lead[r + 1] - lead[r] : 0);
+        for (int k = b + lane; k < e; k += 32) {
+            const int32_t cv = col[k];
+            if (cv < 0) atomicOr(&g_seg_status, STATUS_BAD_CSR);
+            entries[d + (k - b)] = cv | (term ? (int32_t)0x80000000 : 0);
+            vperm[d + (k - b)] = value_base + k;
+        }
+    }
+}
+
+template <typename T>
+__global__ void permute_values_kernel(const int32_t *vperm, int64_t total, int64_t nnz0, const T *val0,
+                                      const T *val1, T *out) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)blockDim.x * gridDim.x) {
+        const int32_t k = vperm[i];
+        out[i] = k < nnz0 ? val0[k] : val1[k - nnz0];
+    }
+}
+
+template <typename V>
+static int upload(V **dev, const std::vector<V> &host) {
+    *dev = nullptr;
+    if (host.empty()) return CGNN_OK;
+    CGNN_CUDA(cudaMalloc(dev, sizeof(V) * host.size()));
+    CGNN_CUDA(cudaMemcpy(*dev, host.data(), sizeof(V) * host.size(), cudaMemcpyHostToDevice));
+    return CGNN_OK;
+}
+
+int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *const col[2], int split,
+               cudaStream_t stream) {
     const int64_t rows = p->rows;
     std::vector<int32_t> h[2];
     for (int t = 0; t < p->nterms; ++t) {
         h[t].resize((size_t)rows + 1);
-        CGNN_CUDA(cudaMemcpyAsync(h[t].data(), p->rowptr[t], sizeof(int32_t) * ((size_t)rows + 1),
+        CGNN_CUDA(cudaMemcpyAsync(h[t].data(), rowptr[t], sizeof(int32_t) * ((size_t)rows + 1),
                                   cudaMemcpyDeviceToHost, stream));
     }
     CGNN_CUDA(cudaStreamSynchronize(stream));
@@ -588,6 +544,7 @@ int plan_analyze(cgnn_plan *p, int split, cudaStream_t stream) {
                      h[t][rows], (long long)p->nnz[t], t);
     }
     const int64_t total = p->nnz[0] + p->nnz[1];
+    p->total = total;
     if (split <= 0) {
         // Degree histogram in one number: rows are short on average -> short chunks keep the
         // tail of a power-law row small; rows are long on average (bucket segments) ->
@@ -596,53 +553,72 @@ int plan_analyze(cgnn_plan *p, int split, cudaStream_t stream) {
         split = avg > 64.0 ? 128 : 64;
     }
     p->split = split;
-    std::vector<int4> longs, items;
-    std::vector<int32_t> row_ids;
-    int64_t short_nonempty = 0;
+    auto degree = [&](int64_t r) {
+        int64_t d = h[0][r + 1] - h[0][r];
+        if (p->nterms > 1) d += h[1][r + 1] - h[1][r];
+        return d;
+    };
+    int64_t short_nonempty = 0, long_rows = 0;
     for (int64_t r = 0; r < rows; ++r) {
-        int64_t deg = 0;
-        for (int t = 0; t < p->nterms; ++t) deg += h[t][r + 1] - h[t][r];
-        if (deg > split) {
-            const int first = (int)items.size();
-            for (int t = 0; t < p->nterms; ++t)
-                for (int e = h[t][r]; e < h[t][r + 1]; e += split)
-                    items.push_back(make_int4((int)longs.size(), t, e,
-                                              (int)std::min<int64_t>((int64_t)e + split, h[t][r + 1])));
-            longs.push_back(make_int4((int)r, first, (int)items.size() - first, 0));
-        } else if (deg > 0) {
-            ++short_nonempty;
-        }
+        const int64_t d = degree(r);
+        if (d > split) ++long_rows;
+        else if (d > 0) ++short_nonempty;
     }
+    p->compact = rows >= 1024 && short_nonempty * 2 < rows ? 1 : 0;
+    const bool identity = !p->compact && long_rows == 0;
+    std::vector<int32_t> dst((size_t)rows, 0), uptr, urow;
+    std::vector<int4> items, longs;
+    int64_t pos = 0;
+    for (int64_t r = 0; r < rows; ++r) {
+        const int64_t d = degree(r);
+        if (d > split || (p->compact && d == 0)) continue;
+        uptr.push_back((int32_t)pos);
+        if (!identity) urow.push_back((int32_t)r);
+        dst[r] = (int32_t)pos;
+        pos += d;
+    }
+    uptr.push_back((int32_t)pos);
+    p->n_direct = (int64_t)uptr.size() - 1;
+    for (int64_t r = 0; r < rows; ++r) {
+        const int64_t d = degree(r);
+        if (d <= split) continue;
+        const int first = (int)items.size();
+        for (int64_t o = 0; o < d; o += split)
+            items.push_back(make_int4((int)longs.size(), (int)(pos + o), (int)(pos + std::min<int64_t>(o + split, d)), 0));
+        longs.push_back(make_int4((int)r, first, (int)items.size() - first, (int)pos));
+        dst[r] = (int32_t)pos;
+        pos += d;
+    }
+    CGNN_REQUIRE(pos == total, "plan: internal entry count mismatch");
     p->n_long = (int64_t)longs.size();
     p->n_items = (int64_t)items.size();
-    const bool compact = rows >= 1024 && short_nonempty * 2 < rows;
-    if (compact) {
-        row_ids.reserve((size_t)short_nonempty);
-        for (int64_t r = 0; r < rows; ++r) {
-            int64_t deg = 0;
-            for (int t = 0; t < p->nterms; ++t) deg += h[t][r + 1] - h[t][r];
-            if (deg > 0 && deg <= split) row_ids.push_back((int32_t)r);
-        }
-        p->n_direct = short_nonempty;
-        if (short_nonempty > 0) {
-            CGNN_CUDA(cudaMalloc(&p->row_ids, sizeof(int32_t) * row_ids.size()));
-            CGNN_CUDA(cudaMemcpy(p->row_ids, row_ids.data(), sizeof(int32_t) * row_ids.size(),
-                                 cudaMemcpyHostToDevice));
-        } else {
-            // Nothing short to do, but the list must still be "present" so that a fresh
-            // output is cleared: keep a one-element dummy.
-            CGNN_CUDA(cudaMalloc(&p->row_ids, sizeof(int32_t)));
-        }
-    } else {
-        p->n_direct = rows;
+    int rc = upload(&p->uptr, uptr);
+    if (rc == CGNN_OK) rc = upload(&p->urow, urow);
+    if (rc == CGNN_OK) rc = upload(&p->items, items);
+    if (rc == CGNN_OK) rc = upload(&p->longs, longs);
+    if (rc != CGNN_OK || total == 0) return rc;
+    int32_t *dst_dev = nullptr;
+    rc = upload(&dst_dev, dst);
+    if (rc != CGNN_OK) return rc;
+    if (cudaMalloc(&p->entries, sizeof(int32_t) * (size_t)total) != cudaSuccess ||
+        cudaMalloc(&p->vperm, sizeof(int32_t) * (size_t)total) != cudaSuccess) {
+        cudaFree(dst_dev);
+        set_error("plan: device allocation failed");
+        return CGNN_ERR_CUDA;
     }
-    if (!items.empty()) {
-        CGNN_CUDA(cudaMalloc(&p->items, sizeof(int4) * items.size()));
-        CGNN_CUDA(cudaMemcpy(p->items, items.data(), sizeof(int4) * items.size(),
-                             cudaMemcpyHostToDevice));
-        CGNN_CUDA(cudaMalloc(&p->longs, sizeof(int4) * longs.size()));
-        CGNN_CUDA(cudaMemcpy(p->longs, longs.data(), sizeof(int4) * longs.size(),
-                             cudaMemcpyHostToDevice));
+    const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 8), 148 * 16));
+    for (int t = 0; t < p->nterms; ++t) {
+        if (p->nnz[t] == 0) continue;
+        scatter_entries_kernel<<<blocks, 256, 0, stream>>>(rowptr[t], col[t], dst_dev, t ? rowptr[0] : nullptr,
+                                                           rows, t, t ? (int32_t)p->nnz[0] : 0, p->entries,
+                                                           p->vperm);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    cudaFree(dst_dev);
+    if (e != cudaSuccess) {
+        set_error("plan: entry scatter failed: %s", cudaGetErrorString(e));
+        return CGNN_ERR_CUDA;
     }
     return CGNN_OK;
 }
@@ -679,7 +655,8 @@ extern "C" {
 
 int cgnn_plan_create(cgnn_plan **plan_out, int64_t rows, int index_bytes, const void *rowptr0,
                      const void *col0, int64_t nnz0, const void *rowptr1, const void *col1,
-                     int64_t nnz1, int split, cgnn_stream_t stream) {
+                     int64_t nnz1, int split, cgnn_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
     CGNN_REQUIRE(plan_out != nullptr, "plan: null output");
     *plan_out = nullptr;
     CGNN_REQUIRE(index_bytes == 4 || index_bytes == 8, "plan: index_bytes must be 4 or 8");
@@ -690,27 +667,37 @@ int cgnn_plan_create(cgnn_plan **plan_out, int64_t rows, int index_bytes, const 
     CGNN_REQUIRE(col0 != nullptr || nnz0 == 0, "plan: null col");
     CGNN_REQUIRE(split >= 0, "plan: negative split");
     cgnn_plan *p = new cgnn_plan();
-    CGNN_CUDA(cudaGetDevice(&p->device));
     p->rows = rows;
     p->nterms = rowptr1 ? 2 : 1;
     p->nnz[0] = nnz0;
     p->nnz[1] = rowptr1 ? nnz1 : 0;
     const void *rp[2] = {rowptr0, rowptr1};
     const void *cl[2] = {col0, col1};
-    int rc = CGNN_OK;
+    int32_t *rp32[2] = {nullptr, nullptr}, *cl32[2] = {nullptr, nullptr};
+    int rc = cudaGetDevice(&p->device) == cudaSuccess ? CGNN_OK : CGNN_ERR_CUDA;
     for (int t = 0; t < p->nterms && rc == CGNN_OK; ++t) {
-        if (cudaMalloc(&p->rowptr[t], sizeof(int32_t) * ((size_t)rows + 1)) != cudaSuccess ||
-            cudaMalloc(&p->col[t], sizeof(int32_t) * (size_t)std::max<int64_t>(p->nnz[t], 1)) !=
-                cudaSuccess) {
+        if (cudaMalloc(&rp32[t], sizeof(int32_t) * ((size_t)rows + 1)) != cudaSuccess ||
+            cudaMalloc(&cl32[t], sizeof(int32_t) * (size_t)std::max<int64_t>(p->nnz[t], 1)) != cudaSuccess) {
             set_error("plan: device allocation failed");
             rc = CGNN_ERR_CUDA;
             break;
         }
-        rc = convert_index(rp[t], index_bytes, p->rowptr[t], rows + 1, (cudaStream_t)stream);
-        if (rc == CGNN_OK)
-            rc = convert_index(cl[t], index_bytes, p->col[t], p->nnz[t], (cudaStream_t)stream);
+        rc = convert_index(rp[t], index_bytes, rp32[t], rows + 1, stream);
+        if (rc == CGNN_OK) rc = convert_index(cl[t], index_bytes, cl32[t], p->nnz[t], stream);
     }
-    if (rc == CGNN_OK) rc = plan_analyze(p, split, (cudaStream_t)stream);
+    if (rc == CGNN_OK) rc = plan_build(p, rp32, cl32, split, stream);
+    for (int t = 0; t < 2; ++t) {
+        if (rp32[t]) cudaFree(rp32[t]);
+        if (cl32[t]) cudaFree(cl32[t]);
+    }
+    if (rc == CGNN_OK) {
+        int status = 0;
+        rc = segreduce_status(&status);
+        if (rc == CGNN_OK && (status & STATUS_BAD_CSR)) {
+            set_error("plan: an index is negative or exceeds 32 bits");
+            rc = CGNN_ERR_INVALID;
+        }
+    }
     if (rc != CGNN_OK) {
         cgnn_plan_destroy(p);
         return rc;
@@ -721,26 +708,40 @@ int cgnn_plan_create(cgnn_plan **plan_out, int64_t rows, int index_bytes, const 
 
 void cgnn_plan_destroy(cgnn_plan *p) {
     if (!p) return;
-    for (int t = 0; t < 2; ++t) {
-        if (p->rowptr[t]) cudaFree(p->rowptr[t]);
-        if (p->col[t]) cudaFree(p->col[t]);
-    }
-    if (p->items) cudaFree(p->items);
-    if (p->longs) cudaFree(p->longs);
-    if (p->row_ids) cudaFree(p->row_ids);
+    void *owned[] = {p->entries, p->vperm, p->uptr, p->urow, p->items, p->longs};
+    for (void *q : owned)
+        if (q) cudaFree(q);
     delete p;
 }
 
 int cgnn_plan_info(const cgnn_plan *p, int64_t info[8]) {
     CGNN_REQUIRE(p != nullptr && info != nullptr, "plan info: null argument");
     info[0] = p->rows;
-    info[1] = p->nnz[0] + p->nnz[1];
+    info[1] = p->total;
     info[2] = p->split;
     info[3] = p->n_long;
     info[4] = p->n_items;
     info[5] = p->n_direct;
     info[6] = p->nterms;
-    info[7] = p->row_ids ? 1 : 0;
+    info[7] = p->compact;
+    return CGNN_OK;
+}
+
+int cgnn_plan_permute_values(const cgnn_plan *p, int dtype, const void *val0, const void *val1,
+                             void *out, cgnn_stream_t stream) {
+    CGNN_REQUIRE(p != nullptr, "permute_values: null plan");
+    CGNN_REQUIRE(dtype == CGNN_F32 || dtype == CGNN_F64, "permute_values: unknown dtype %d", dtype);
+    if (p->total == 0) return CGNN_OK;
+    CGNN_REQUIRE(out != nullptr && (val0 != nullptr || p->nnz[0] == 0) &&
+                     (val1 != nullptr || p->nnz[1] == 0), "permute_values: null pointer");
+    const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(p->total, 256), 148 * 16);
+    if (dtype == CGNN_F32)
+        permute_values_kernel<float><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+            p->vperm, p->total, p->nnz[0], (const float *)val0, (const float *)val1, (float *)out);
+    else
+        permute_values_kernel<double><<<blocks, 256, 0, (cudaStream_t)stream>>>(
+            p->vperm, p->total, p->nnz[0], (const double *)val0, (const double *)val1, (double *)out);
+    CGNN_LAUNCH_CHECK();
     return CGNN_OK;
 }
 
@@ -763,15 +764,15 @@ int cgnn_spmm(const cgnn_plan *plan, int dtype, int64_t width, const void *val, 
               void *out, int accumulate, void *scratch, size_t scratch_bytes,
               cgnn_stream_t stream) {
     CGNN_REQUIRE(plan != nullptr && plan->nterms == 1, "spmm: plan must hold one block");
-    return run(plan, dtype, width, val, src, nullptr, nullptr, nullptr, nullptr, nullptr, out, accumulate,
+    return run(plan, dtype, width, val, src, nullptr, nullptr, nullptr, nullptr, out, accumulate,
                scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
-int cgnn_spmm_pair(const cgnn_plan *plan, int dtype, int64_t width, const void *val0,
-                   const void *src0, const void *val1, const void *src1, void *out,
-                   int accumulate, void *scratch, size_t scratch_bytes, cgnn_stream_t stream) {
+int cgnn_spmm_pair(const cgnn_plan *plan, int dtype, int64_t width, const void *val,
+                   const void *src0, const void *src1, void *out, int accumulate, void *scratch,
+                   size_t scratch_bytes, cgnn_stream_t stream) {
     CGNN_REQUIRE(plan != nullptr && plan->nterms == 2, "spmm_pair: plan must hold two blocks");
-    return run(plan, dtype, width, val0, src0, val1, src1, nullptr, nullptr, nullptr, out, accumulate,
+    return run(plan, dtype, width, val, src0, src1, nullptr, nullptr, nullptr, out, accumulate,
                scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
@@ -780,7 +781,7 @@ int cgnn_cluster_mean(const cgnn_plan *plan, int dtype, int64_t width, const voi
                       cgnn_stream_t stream) {
     CGNN_REQUIRE(plan != nullptr && plan->nterms == 1, "cluster_mean: bad plan");
     CGNN_REQUIRE(count != nullptr, "cluster_mean: null counts");
-    return run(plan, dtype, width, nullptr, x, nullptr, nullptr, nullptr, nullptr, count, out, 0, scratch,
+    return run(plan, dtype, width, nullptr, x, nullptr, nullptr, nullptr, count, out, 0, scratch,
                scratch_bytes, (cudaStream_t)stream);
 }
 
@@ -792,7 +793,7 @@ int cgnn_cluster_reconstruct_backward(const cgnn_plan *plan, int dtype, int64_t 
     CGNN_REQUIRE(relu >= 0 && relu <= 2, "reconstruct_backward: relu mode must be 0, 1 or 2");
     CGNN_REQUIRE(!relu || output != nullptr || plan->nnz[0] == 0,
                  "reconstruct_backward: relu needs the forward output");
-    int rc = run(plan, dtype, width, nullptr, grad, nullptr, nullptr, relu == 1 ? output : nullptr,
+    int rc = run(plan, dtype, width, nullptr, grad, nullptr, relu == 1 ? output : nullptr,
                  relu == 2 ? output : nullptr, nullptr, d_reps, 0, scratch, scratch_bytes,
                  (cudaStream_t)stream);
     if (rc != CGNN_OK || bias_grad == nullptr || width == 0) return rc;

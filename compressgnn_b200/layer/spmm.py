@@ -38,8 +38,11 @@ def _forward(graph, x, record=None):
     x = x.contiguous()
     plan = graph.propagation_plan()
     dt = x.dtype
-    rule_out = _timed(record, "fwd_r2v", lambda: _native.spmm_with_plan(
-        plan.r2v, graph.r2v_graph.value_as(dt), x))
+    # rule_out is placed a whole number of rows away from x so that the fused pass over
+    # (rule_out, x) addresses both matrices with one base pointer
+    rule_out = _native.empty_row_aligned(graph.rule_cnt, x)
+    _timed(record, "fwd_r2v", lambda: _native.spmm_with_plan(
+        plan.r2v, graph.r2v_graph.value_as(dt), x, out=rule_out))
     for i, (level_plan, level) in enumerate(zip(plan.levels, graph.r2r_graph)):
         _timed(record, f"fwd_level{i}", lambda: _native.spmm_with_plan(
             level_plan, level.value_as(dt), rule_out, out=rule_out, accumulate=True))
@@ -52,8 +55,9 @@ def _backward(graph, grad, record=None):
     grad = grad.contiguous()
     plan = graph.propagation_plan()
     dt = grad.dtype
-    rule_out = _timed(record, "bwd_v2r_t", lambda: _native.spmm_with_plan(
-        plan.v2r_t, graph.v2r_graph.value_as(dt, True), grad))
+    rule_out = _native.empty_row_aligned(graph.rule_cnt, grad)
+    _timed(record, "bwd_v2r_t", lambda: _native.spmm_with_plan(
+        plan.v2r_t, graph.v2r_graph.value_as(dt, True), grad, out=rule_out))
     levels = list(enumerate(zip(plan.levels_t, graph.r2r_graph)))
     for i, (level_plan, level) in reversed(levels):
         _timed(record, f"bwd_level{i}", lambda: _native.spmm_with_plan(

@@ -57,6 +57,7 @@ class SegmentPlan:
         self._handle = handle
         self.device = device
         self._scratch = {}
+        self._values = _TensorKeyedCache(limit=8)
         info = (ctypes.c_int64 * 8)()
         check(lib().cgnn_plan_info(handle, info))
         (self.rows, self.nnz, self.split, self.long_rows, self.chunks, self.direct_units,
@@ -100,6 +101,23 @@ class SegmentPlan:
                                                     int(groups), int(split),
                                                     _stream_ptr(index.device)))
         return cls(handle.value, index.device)
+
+    def values(self, val0, val1=None):
+        """``val0`` (and ``val1`` of the second block) brought into the plan's entry order; the
+        result is cached for as long as the given tensors live and stay unmodified."""
+        tensors = (val0,) if val1 is None else (val0, val1)
+        cached = self._values.get(tensors)
+        if cached is None:
+            _require(sum(t.numel() for t in tensors) == self.nnz, "values do not match the plan's entries")
+            cached = torch.empty(self.nnz, dtype=val0.dtype, device=self.device)
+            if self.nnz:
+                with torch.cuda.device(self.device):
+                    check(lib().cgnn_plan_permute_values(
+                        self.handle, _dtype_code(val0, "values"), _ptr(val0.contiguous()),
+                        _ptr(val1.contiguous()) if val1 is not None else None, _ptr(cached),
+                        _stream_ptr(self.device)))
+            self._values.put(tensors, cached)
+        return cached
 
     def scratch(self, width, dtype_code):
         """(pointer, bytes) of this plan's scratch for launches ``width`` columns wide on the
@@ -187,7 +205,8 @@ def index_plan(index, groups):
 # spmm_func  (ref: src/runtime/csrc/sparse/spmm.cpp:11-23, cuda/spmm_gpu.cu:8-107)
 # -----------------------------------------------------------------------------------------
 def spmm_with_plan(plan, value, mat, out=None, accumulate=False):
-    """``out (+)= A @ mat`` for the CSR block behind ``plan``; ``value`` may be None (ones)."""
+    """``out (+)= A @ mat`` for the CSR block behind ``plan``; ``value`` is the block's value
+    array in its original CSR order, or None (ones)."""
     code = _dtype_code(mat, "spmm")
     width = mat.size(-1)
     if out is None:
@@ -198,10 +217,23 @@ def spmm_with_plan(plan, value, mat, out=None, accumulate=False):
     if plan.nnz == 0:
         return out if accumulate else out.zero_()
     sp, sb = plan.scratch(width, code)
+    if value is not None:
+        value = plan.values(value)
     with torch.cuda.device(mat.device):
         check(lib().cgnn_spmm(plan.handle, code, width, _ptr(value), _ptr(mat), _ptr(out),
                               1 if accumulate else 0, sp, sb, _stream_ptr(mat.device)))
     return out
+
+
+def empty_row_aligned(rows, like):
+    """A ``[rows, like.size(1)]`` tensor whose first row starts a whole number of rows away from
+    ``like``'s first row, so that the fused two-block pass can address both with one base
+    pointer and a row index (see ``cgnn_spmm_pair``)."""
+    width = like.size(1)
+    buf = torch.empty(rows * width + width, dtype=like.dtype, device=like.device)
+    row_bytes = width * like.element_size()
+    shift = ((like.data_ptr() - buf.data_ptr()) % row_bytes) // like.element_size() if row_bytes else 0
+    return buf[shift:shift + rows * width].view(rows, width)
 
 
 def spmm_pair_with_plan(plan, value0, mat0, value1, mat1, out=None, accumulate=False):
@@ -215,9 +247,10 @@ def spmm_pair_with_plan(plan, value0, mat0, value1, mat1, out=None, accumulate=F
     if out.numel() == 0:
         return out
     sp, sb = plan.scratch(width, code)
+    value = plan.values(value0, value1)
     with torch.cuda.device(mat0.device):
-        check(lib().cgnn_spmm_pair(plan.handle, code, width, _ptr(value0), _ptr(mat0), _ptr(value1),
-                                   _ptr(mat1), _ptr(out), 1 if accumulate else 0, sp, sb,
+        check(lib().cgnn_spmm_pair(plan.handle, code, width, _ptr(value), _ptr(mat0), _ptr(mat1),
+                                   _ptr(out), 1 if accumulate else 0, sp, sb,
                                    _stream_ptr(mat0.device)))
     return out
 

@@ -61,9 +61,16 @@ int cgnn_plan_create_from_index(cgnn_plan **plan_out, const int64_t *index, int6
 
 void cgnn_plan_destroy(cgnn_plan *plan);
 
-/* info[0..7] = rows, nnz (both terms), split, long rows, chunks, direct work units,
- * terms, 1 if a compact row list is used. */
+/* info[0..7] = rows, entries (both terms), split, long rows, chunks, rows in the direct
+ * list, terms, 1 if empty rows are left out of the list. */
 int cgnn_plan_info(const cgnn_plan *plan, int64_t info[8]);
+
+/* A plan keeps its entries in its own order (short rows back to back, then the chunks of
+ * long rows; for two blocks a row's entries of block 0 precede those of block 1).  This
+ * brings the caller's value arrays (val0[nnz0], val1[nnz1] or NULL) into that order:
+ * out[nnz0+nnz1].  Done once per graph; cgnn_spmm / cgnn_spmm_pair take the result. */
+int cgnn_plan_permute_values(const cgnn_plan *plan, int dtype, const void *val0,
+                             const void *val1, void *out, cgnn_stream_t stream);
 
 /* Bytes of caller-provided scratch a launch over `width` columns needs.  The first
  * cgnn_plan_ticket_bytes() bytes hold chunk tickets: they must be zero before the first
@@ -76,7 +83,8 @@ size_t cgnn_plan_ticket_bytes(const cgnn_plan *plan, int64_t width, int dtype);
  * SpMM:  out[r,:] (+)= sum_e val[e] * src[col[e],:]
  * ref: spmm_func, src/runtime/csrc/sparse/spmm.cpp:11-23 and
  *      src/runtime/csrc/sparse/cuda/spmm_gpu.cu:8-107 (all six kernel variants).
- * val may be NULL (all ones).  accumulate != 0 adds to the existing out (the reference's
+ * val holds the entry values IN PLAN ORDER (cgnn_plan_permute_values) or is NULL (all
+ * ones).  accumulate != 0 adds to the existing out (the reference's
  * optional_out contract); out may alias src when the rows written are never read (the
  * in-place rule-level updates of ref: layer/CompressgnnSPMM.py:57-58).
  * ------------------------------------------------------------------------------------- */
@@ -86,12 +94,14 @@ int cgnn_spmm(const cgnn_plan *plan, int dtype, int64_t width, const void *val,
 
 /* Two blocks over the same output rows in one pass:
  *   out[r,:] (+)= sum_e val0[e]*src0[col0[e],:] + sum_e val1[e]*src1[col1[e],:]
- * (the plan must have been built with two terms).  Fuses the last two calls of the
+ * (the plan must have been built with two terms; val = both value arrays in plan order).
+ * Fastest when src1 starts a whole number of rows (width elements) away from src0, which a
+ * caller that allocates one of the two can arrange; any other placement works, slower.  Fuses the last two calls of the
  * reference's forward (v2r then v2v, ref: layer/CompressgnnSPMM.py:59-60) and of its
  * backward (:84-85) so that out is written once. */
-int cgnn_spmm_pair(const cgnn_plan *plan, int dtype, int64_t width, const void *val0,
-                   const void *src0, const void *val1, const void *src1, void *out,
-                   int accumulate, void *scratch, size_t scratch_bytes, cgnn_stream_t stream);
+int cgnn_spmm_pair(const cgnn_plan *plan, int dtype, int64_t width, const void *val,
+                   const void *src0, const void *src1, void *out, int accumulate,
+                   void *scratch, size_t scratch_bytes, cgnn_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------
  * LSH cluster assignment.
