@@ -29,6 +29,7 @@ SIGNATURES = {
     "cgnn_plan_ticket_bytes": (_c_size, [_c_ptr, _c_i64, _c_int]),
     "cgnn_spmm": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,
                            _c_size, _c_ptr]),
+    "cgnn_spmm_static_scratch": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]),
     "cgnn_spmm_pair": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
                                 _c_ptr, _c_size, _c_ptr]),
     "cgnn_plan_permute_values": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),

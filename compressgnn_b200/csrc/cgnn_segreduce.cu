@@ -14,6 +14,7 @@
 //     ticket adds the partials in chunk order -- deterministic, no float atomics, and no
 //     unit ever waits for another.
 #include <algorithm>
+#include <mutex>
 #include <vector>
 
 #include "cgnn_plan.h"
@@ -39,6 +40,12 @@
 #endif
 
 namespace cgnn {
+
+// Scratch of cgnn_spmm_static_scratch: lives in the library image, so every GPU that loads the
+// library holds CGNN_STATIC_SCRATCH_BYTES of it until the process exits.  In host code this
+// name is only a stand-in for the symbol, never a device address; the address is looked up
+// per device with cudaGetSymbolAddress (static_scratch_pointer below).
+static __device__ __align__(256) unsigned char g_static_scratch[CGNN_STATIC_SCRATCH_BYTES];
 
 static __device__ int g_seg_status = 0;
 
@@ -647,11 +654,52 @@ static int convert_index(const void *in, int index_bytes, int32_t *out, int64_t 
     return CGNN_OK;
 }
 
+// Device address of g_static_scratch on the current device, looked up once per device.
+static int static_scratch_pointer(int device, void **out) {
+    constexpr int MAX_DEVICES = 64;
+    static std::mutex lock;
+    static void *address[MAX_DEVICES] = {};
+    CGNN_REQUIRE(device >= 0 && device < MAX_DEVICES, "static scratch: device ordinal %d not supported", device);
+    std::lock_guard<std::mutex> guard(lock);
+    if (address[device] == nullptr) {
+        void *p = nullptr;
+        CGNN_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        address[device] = p;
+    }
+    *out = address[device];
+    return CGNN_OK;
+}
+
 }  // namespace cgnn
 
 using namespace cgnn;
 
 extern "C" {
+
+int cgnn_spmm_static_scratch(const cgnn_plan *plan, int dtype, int64_t width, const void *val,
+                             const void *src, void *out, int accumulate, cgnn_stream_t stream) {
+    CGNN_REQUIRE(plan != nullptr && plan->nterms == 1, "spmm_static_scratch: plan must hold one block");
+    CGNN_REQUIRE(dtype == CGNN_F32 || dtype == CGNN_F64, "spmm_static_scratch: unknown dtype %d", dtype);
+    CGNN_REQUIRE(width >= 0, "spmm_static_scratch: negative width");
+    int device = -1;
+    CGNN_CUDA(cudaGetDevice(&device));
+    CGNN_REQUIRE(device == plan->device, "spmm_static_scratch: the plan was built on device %d, current is %d",
+                 plan->device, device);
+    const size_t ticket_bytes = cgnn_plan_ticket_bytes(plan, width, dtype);
+    const size_t need = ticket_bytes + (size_t)plan->n_items * (size_t)width * (dtype == CGNN_F64 ? 8 : 4);
+    CGNN_REQUIRE(need <= (size_t)CGNN_STATIC_SCRATCH_BYTES,
+                 "spmm_static_scratch: this plan and width need %zu bytes of scratch, the built-in "
+                 "buffer holds %zu; use cgnn_spmm with caller-provided scratch",
+                 need, (size_t)CGNN_STATIC_SCRATCH_BYTES);
+    void *scratch = nullptr;
+    int rc = static_scratch_pointer(device, &scratch);
+    if (rc != CGNN_OK) return rc;
+    // The buffer keeps whatever the previous call left; the ticket words must start at zero.
+    if (plan->n_items > 0 && ticket_bytes > 0)
+        CGNN_CUDA(cudaMemsetAsync(scratch, 0, ticket_bytes, (cudaStream_t)stream));
+    return run(plan, dtype, width, val, src, nullptr, nullptr, nullptr, nullptr, out, accumulate,
+               scratch, (size_t)CGNN_STATIC_SCRATCH_BYTES, (cudaStream_t)stream);
+}
 
 int cgnn_plan_create(cgnn_plan **plan_out, int64_t rows, int index_bytes, const void *rowptr0,
                      const void *col0, int64_t nnz0, const void *rowptr1, const void *col1,

@@ -92,6 +92,30 @@ int cgnn_spmm(const cgnn_plan *plan, int dtype, int64_t width, const void *val,
               const void *src, void *out, int accumulate, void *scratch,
               size_t scratch_bytes, cgnn_stream_t stream);
 
+/* cgnn_spmm for callers that cannot allocate.  (No counterpart in the reference, whose
+ * operators allocate through torch on every call.)
+ *
+ * Some hosts cannot hand cgnn_spmm a scratch buffer because they cannot create one when the
+ * call is made: a serving process that gave the whole GPU to its own memory pool at start-up,
+ * so that any further cudaMalloc fails; or a latency-critical loop that must never run into
+ * the device-wide synchronisation cudaMalloc and cudaFree can cause.  For them the library
+ * carries its own scratch: CGNN_STATIC_SCRATCH_BYTES of device memory inside the library
+ * image, held by every GPU that loads the library until the process exits.
+ *
+ * Same result as cgnn_spmm (bit for bit).  The call allocates nothing -- no cudaMalloc,
+ * cudaFree or allocating library routine.  Limits and rules:
+ *   - plans whose chunk partial sums for `width` do not fit in CGNN_STATIC_SCRATCH_BYTES
+ *     (cgnn_plan_scratch_bytes tells) are rejected with CGNN_ERR_INVALID and a message;
+ *   - the buffer is shared by every call on a device and keeps the previous call's contents;
+ *     each call clears the ticket words it needs itself, but two calls that overlap on the
+ *     GPU (different streams, no dependency) race on it -- order them;
+ *   - the first call on each device looks up the buffer's address with that device current;
+ *     make that first call outside of any stream capture;
+ *   - the plan must have been created on the current device. */
+#define CGNN_STATIC_SCRATCH_BYTES (8u << 20)
+int cgnn_spmm_static_scratch(const cgnn_plan *plan, int dtype, int64_t width, const void *val,
+                             const void *src, void *out, int accumulate, cgnn_stream_t stream);
+
 /* Two blocks over the same output rows in one pass:
  *   out[r,:] (+)= sum_e val0[e]*src0[col0[e],:] + sum_e val1[e]*src1[col1[e],:]
  * (the plan must have been built with two terms; val = both value arrays in plan order).
