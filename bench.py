@@ -346,6 +346,105 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_cluster(args):
+    """Config 3: Compressgnn_Cluster -> Linear(128->256) on representatives -> fused reconstruct
+    (bias + ReLU), forward + backward, 2.45 M nodes drawn from 4096 Gaussian centroids, H=16,
+    refresh_interval=5.  A step = one epoch.  Per-operator CUDA-event times and algorithmic GB/s
+    are reported next to the epoch time; the CPU leg runs the reference's cluster_forward
+    plus the torch CPU formulas its layers use."""
+    import torch
+    from compressgnn_b200 import runtime as rt
+    from compressgnn_b200.layer import Compressgnn_Cluster, Compressgnn_Reconstruct
+    torch.cuda.set_device(0)
+    n, width, out_width, bits = args.cluster_nodes, 128, 256, 16
+    gen = torch.Generator(device="cuda").manual_seed(3)
+    cent = torch.randn(4096, width, device="cuda", generator=gen)
+    which = torch.randint(0, 4096, (n,), device="cuda", generator=gen)
+    x = (cent[which] + 0.1 * torch.randn(n, width, device="cuda", generator=gen)).requires_grad_()
+    del which
+    torch.manual_seed(3)
+    cluster = Compressgnn_Cluster(width, bits, device="cuda", refresh_interval=5)
+    lin = torch.nn.Linear(width, out_width).cuda()
+    reconstruct = Compressgnn_Reconstruct()
+    grad_out = torch.randn(n, out_width, device="cuda", generator=gen)
+
+    def epoch(e):
+        cluster.set_epoch(e)
+        reps, index = cluster(x)
+        y = reconstruct(torch.nn.functional.linear(reps, lin.weight, None), index, bias=lin.bias, activation="relu")
+        y.backward(grad_out)
+        x.grad = None
+        return y
+
+    for e in range(max(args.warmup, 3)):
+        epoch(e)
+    cluster.reset_cache()
+    cluster.refresh_count = 0
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(0) as clocks:
+        start.record()
+        for e in range(args.steps):
+            epoch(e)
+        stop.record()
+        torch.cuda.synchronize()
+    ms_epoch = start.elapsed_time(stop) / args.steps
+
+    # per-operator timings on the same tensors (CUDA events, median of 20)
+    def timed(fn, reps_=20):
+        for _ in range(3):
+            fn()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps_)]
+        for a, b in ev:
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        return sorted(a.elapsed_time(b) for a, b in ev)[reps_ // 2]
+
+    xd = x.detach()
+    ws = rt.cluster_workspace(xd, bits)
+    ids, counts, active = rt.cluster_assign(xd, cluster.random_vectors, bits, ws)
+    groups = active + 1
+    reps = rt.cluster_mean(xd, ids, counts)
+    table = torch.randn(groups, out_width, device="cuda", generator=gen)
+    bias = torch.randn(out_width, device="cuda", generator=gen)
+    y = rt.cluster_reconstruct(table, ids, bias, True)
+    g_small = torch.randn(groups, width, device="cuda", generator=gen)
+    ops = {
+        "cluster_assign (projection+codes+compaction)": (lambda: rt.cluster_assign(xd, cluster.random_vectors, bits, ws),
+                                                          4 * n * width + 4 * width * bits + 8 * n + 40 * n),
+        "cluster_mean": (lambda: rt.cluster_mean(xd, ids, counts), 4 * n * width + 8 * n + 4 * groups * width),
+        "cluster_mean_backward": (lambda: rt.cluster_mean_backward(g_small, ids, counts),
+                                  4 * groups * width + 8 * n + 4 * n * width),
+        "cluster_reconstruct (bias+relu)": (lambda: rt.cluster_reconstruct(table, ids, bias, True),
+                                            4 * groups * out_width + 8 * n + 4 * out_width + 4 * n * out_width),
+        "cluster_reconstruct_backward (relu, exact mask)": (
+            lambda: rt.cluster_reconstruct_backward(grad_out, ids, y, groups, True),
+            8 * n * out_width + 8 * n + 4 * groups * out_width),
+        "cluster_reconstruct_backward (relu, one mask row per group)": (
+            lambda: rt.cluster_reconstruct_backward(grad_out, ids, y, groups, True, output_is_forward_result=True),
+            4 * n * out_width + 8 * n + 8 * groups * out_width),
+    }
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    peak = json.loads(peaks_path.read_text())["hbm_gbs"] if peaks_path.is_file() else 6650.0
+    op_report = {}
+    for name, (fn, nbytes) in ops.items():
+        ms = timed(fn)
+        op_report[name] = {"ms": ms, "algorithmic_GBps": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / peak}
+    assert rt.device_status() == 0
+    line = {"metric": "cluster_linear_reconstruct_nodes_per_s", "value": n / (ms_epoch * 1e-3) / 1e6, "unit": "Mnode/s",
+            "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_epoch,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "cluster: Compressgnn_Cluster + Linear 128->256 + Compressgnn_Reconstruct(relu), fwd+bwd",
+                       "nodes": n, "feature_width": width, "out_width": out_width, "bits": bits, "centroids": 4096,
+                       "active_buckets": active, "refresh_interval": 5, "refreshes": cluster.refresh_count,
+                       "l2": "inputs larger than L2 (X is %.0f MB)" % (4e-6 * n * width)},
+            "operators": op_report, "peak_GBps": peak, "clocks": clocks.summary(),
+            "gpu_launches": None}
+    print(json.dumps(line))
+
+
 def run_reference(args):
     """The reference's CPU implementation of the same workload, on this box's host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -376,11 +475,14 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["cgnn", "reference"], default="cgnn")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="propagation")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cluster"], default="propagation")
+    ap.add_argument("--cluster-nodes", type=int, default=2450000)
     ap.add_argument("--cpu-steps", type=int, default=3, help="steps of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.workload == "cluster":
+        run_cluster(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)
