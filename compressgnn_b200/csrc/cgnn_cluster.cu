@@ -4,7 +4,7 @@
 //
 // Projection kernel (the only heavy part: it reads all of X once):
 //   * a CTA walks row tiles of TR rows; X arrives in k-chunks of KC columns through a
-//     two-stage cp.async pipeline into padded shared memory (conflict-free 128-bit reads);
+//     multi-stage cp.async pipeline into padded shared memory (conflict-free 128-bit reads);
 //   * each thread owns RPT rows and all `bits` accumulators of them, so the n x bits
 //     projection never leaves registers in the fused path; plane values are broadcast
 //     128-bit shared loads shared by the RPT rows;
@@ -13,6 +13,9 @@
 // Compaction sorts (code,row) pairs with a stable radix sort (CUB), so neither a 2^bits
 // histogram nor any atomic is involved and the permutation is deterministic.
 #include <algorithm>
+#include <mutex>
+#include <type_traits>
+#include <vector>
 #include <cub/cub.cuh>
 
 #include "cgnn_plan.h"
@@ -31,7 +34,11 @@ int cluster_status(int *out) {
 constexpr int PROJ_THREADS = 128;
 constexpr int KC = 16;         // columns per pipeline stage
 constexpr int XS_STRIDE = 20;  // padded row stride of the X stage (elements): odd in 16-byte units
-constexpr int PROJ_CTAS_PER_SM = 5;  // 43 KB of shared memory per CTA at 16 planes
+#ifndef CGNN_PROJ_STAGES
+#define CGNN_PROJ_STAGES 2
+#endif
+constexpr int PROJ_STAGES = CGNN_PROJ_STAGES;   // cp.async pipeline depth
+constexpr int PROJ_CTAS_PER_SM = PROJ_STAGES == 2 ? 5 : 3;  // shared-memory limited at 16 planes
 
 __device__ __forceinline__ void cp_async16(void *smem, const void *gmem, int src_bytes) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -51,8 +58,8 @@ __device__ __forceinline__ void cp_async_wait() {
 template <typename T, int HB, int RPT>
 struct ProjSmem {
     static constexpr int TR = PROJ_THREADS * RPT;
-    T xs[2][TR][XS_STRIDE];
-    T ws[2][KC][HB];
+    T xs[PROJ_STAGES][TR][XS_STRIDE];
+    T ws[PROJ_STAGES][KC][HB];
 };
 
 // Stage loader: X[row0 .. row0+TR, k0 .. k0+KC) and planes[k0 .. k0+KC, 0..bits) -> shared,
@@ -122,26 +129,48 @@ project_kernel(const T *__restrict__ x, const T *__restrict__ planes, int64_t n,
     const int64_t stages = my_tiles * nk;
     if (stages == 0) return;
 
-    T acc[RPT][HB];
-    load_stage<T, HB, RPT>(sm, 0, x, planes, n, width, bits, (int64_t)blockIdx.x * TR, 0, vec_ok);
-    cp_async_commit();
-    for (int64_t s = 0; s < stages; ++s) {
-        const int cur = (int)(s & 1);
-        const int64_t tile = blockIdx.x + (s / nk) * gridDim.x;
-        const int64_t kc = s % nk;
-        if (s + 1 < stages) {
-            const int64_t ntile = blockIdx.x + ((s + 1) / nk) * gridDim.x;
-            load_stage<T, HB, RPT>(sm, cur ^ 1, x, planes, n, width, bits, ntile * TR,
-                                   ((s + 1) % nk) * KC, vec_ok);
+    // fp32 accumulators are kept as pairs of adjacent planes and updated with the packed
+    // two-wide FMA of sm_100 (fma.rn.f32x2): each half is an IEEE fused multiply-add, so the
+    // per-plane chain p = fma(x, w, p) -- and with it every sign bit -- is unchanged, at half
+    // the issue slots.  fp64 uses scalar FMAs.
+    constexpr bool PACKED = sizeof(T) == 4;
+    using Acc = typename std::conditional<PACKED, float2, T>::type;
+    constexpr int NACC = PACKED ? HB / 2 : HB;
+    Acc acc[RPT][NACC];
+    auto plane = [&](int i, int h) -> T {
+        if constexpr (PACKED) return (h & 1) ? acc[i][h >> 1].y : acc[i][h >> 1].x;
+        else return acc[i][h];
+    };
+    // prologue: the first PROJ_STAGES-1 stages are requested up front
+#pragma unroll
+    for (int pre = 0; pre < PROJ_STAGES - 1; ++pre) {
+        if (pre < stages) {
+            const int64_t ptile = blockIdx.x + (pre / nk) * gridDim.x;
+            load_stage<T, HB, RPT>(sm, pre, x, planes, n, width, bits, ptile * TR, (pre % nk) * KC, vec_ok);
         }
         cp_async_commit();
-        cp_async_wait<1>();
+    }
+    for (int64_t s = 0; s < stages; ++s) {
+        const int cur = (int)(s % PROJ_STAGES);
+        const int64_t tile = blockIdx.x + (s / nk) * gridDim.x;
+        const int64_t kc = s % nk;
+        const int64_t ahead = s + PROJ_STAGES - 1;
+        if (ahead < stages) {
+            const int64_t ntile = blockIdx.x + (ahead / nk) * gridDim.x;
+            load_stage<T, HB, RPT>(sm, (int)(ahead % PROJ_STAGES), x, planes, n, width, bits, ntile * TR,
+                                   (ahead % nk) * KC, vec_ok);
+        }
+        cp_async_commit();
+        cp_async_wait<PROJ_STAGES - 1>();
         __syncthreads();
         if (kc == 0) {
 #pragma unroll
             for (int i = 0; i < RPT; ++i)
 #pragma unroll
-                for (int h = 0; h < HB; ++h) acc[i][h] = T(0);
+                for (int h = 0; h < NACC; ++h) {
+                    if constexpr (PACKED) acc[i][h] = make_float2(0.f, 0.f);
+                    else acc[i][h] = T(0);
+                }
         }
 #pragma unroll
         for (int kk = 0; kk < KC; kk += VW) {
@@ -154,11 +183,21 @@ project_kernel(const T *__restrict__ x, const T *__restrict__ planes, int64_t n,
 #pragma unroll
                 for (int h4 = 0; h4 < HB; h4 += VW) {
                     const V w = *reinterpret_cast<const V *>(&sm.ws[cur][kk + q][h4]);
+                    if constexpr (PACKED) {
 #pragma unroll
-                    for (int j = 0; j < VW; ++j)
+                        for (int j = 0; j < VW; j += 2)
 #pragma unroll
-                        for (int i = 0; i < RPT; ++i)
-                            acc[i][h4 + j] = fma(xv[i].v[q], w.v[j], acc[i][h4 + j]);
+                            for (int i = 0; i < RPT; ++i)
+                                acc[i][(h4 + j) >> 1] =
+                                    __ffma2_rn(make_float2(xv[i].v[q], xv[i].v[q]),
+                                               make_float2(w.v[j], w.v[j + 1]), acc[i][(h4 + j) >> 1]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < VW; ++j)
+#pragma unroll
+                            for (int i = 0; i < RPT; ++i)
+                                acc[i][h4 + j] = fma(xv[i].v[q], w.v[j], acc[i][h4 + j]);
+                    }
                 }
             }
         }
@@ -170,13 +209,13 @@ project_kernel(const T *__restrict__ x, const T *__restrict__ planes, int64_t n,
                     if (proj) {
 #pragma unroll
                         for (int h = 0; h < HB; ++h)
-                            if (h < bits) proj[row * bits + h] = acc[i][h];
+                            if (h < bits) proj[row * bits + h] = plane(i, h);
                     }
                     if (codes) {
                         int32_t id = 0;
 #pragma unroll
                         for (int h = 0; h < HB; ++h)
-                            if (h < bits) id = (id << 1) | (acc[i][h] > T(0) ? 1 : 0);
+                            if (h < bits) id = (id << 1) | (plane(i, h) > T(0) ? 1 : 0);
                         codes[row] = id;
                     }
                 }
@@ -351,6 +390,18 @@ __global__ void index_to_key_kernel(const int64_t *index, int64_t n, int64_t gro
     }
 }
 
+// Host copy of the segment starts of the latest cgnn_cluster_assign, handed to the export step.
+struct HostSegments {
+    std::mutex lock;
+    const void *workspace = nullptr;
+    int64_t n = 0, valid = 0;
+    std::vector<int32_t> start;
+};
+static HostSegments &host_segments() {
+    static HostSegments hs;
+    return hs;
+}
+
 static unsigned grid_for(int64_t n) { return (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(n, 256), 148 * 16)); }
 
 // Sort (key,row) pairs by the low `bits` bits of the key; leaves sorted keys in keys_out and
@@ -443,9 +494,21 @@ int cgnn_cluster_assign(const int32_t *codes, int64_t n, int bits, void *workspa
     scatter_ids_kernel<<<grid_for(n), 256, 0, stream>>>(L.vals[0], L.cid, flags, n, ids, L.segstart,
                                                         L.active);
     CGNN_LAUNCH_CHECK();
+    // One synchronisation fetches `active` and, speculatively, the head of the segment-start
+    // array (active <= 2^bits, so 2^bits + 2 entries cover it for the usual bit counts); the
+    // export step then needs no further round trip.
+    HostSegments &hs = host_segments();
+    std::lock_guard<std::mutex> guard(hs.lock);
+    const int64_t want = std::min<int64_t>(n + 2, std::min<int64_t>(((int64_t)1 << bits) + 2, (int64_t)1 << 20));
+    hs.workspace = workspace;
+    hs.n = n;
+    hs.start.resize((size_t)want);
     int32_t active = 0;
     CGNN_CUDA(cudaMemcpyAsync(&active, L.active, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    CGNN_CUDA(cudaMemcpyAsync(hs.start.data(), L.segstart, sizeof(int32_t) * (size_t)want,
+                              cudaMemcpyDeviceToHost, stream));
     CGNN_CUDA(cudaStreamSynchronize(stream));
+    hs.valid = (int64_t)active + 2 <= want ? (int64_t)active + 2 : 0;
     *active_out = active;
     return CGNN_OK;
 }
@@ -472,7 +535,13 @@ int cgnn_cluster_assign_export(const void *workspace, int64_t n, int64_t active,
     p->nnz[0] = n;
     const int32_t *rp[2] = {L.segstart, nullptr};
     const int32_t *cl[2] = {L.vals[0], nullptr};
-    int rc = plan_build(p, rp, cl, split, stream);
+    int rc;
+    {
+        HostSegments &hs = host_segments();
+        std::lock_guard<std::mutex> guard(hs.lock);
+        const bool have = hs.workspace == workspace && hs.n == n && hs.valid == active + 2;
+        rc = plan_build(p, rp, cl, split, stream, have ? hs.start.data() : nullptr, false);
+    }
     if (rc != CGNN_OK) {
         cgnn_plan_destroy(p);
         return rc;
@@ -550,7 +619,7 @@ int cgnn_plan_create_from_index(cgnn_plan **plan_out, const int64_t *index, int6
         }
         const int32_t *rp[2] = {rowptr, nullptr};
         const int32_t *cl[2] = {L.vals[0], nullptr};
-        rc = plan_build(p, rp, cl, split, stream);
+        rc = plan_build(p, rp, cl, split, stream, nullptr, false);
     } while (0);
     if (ws) cudaFree(ws);
     if (hist) cudaFree(hist);

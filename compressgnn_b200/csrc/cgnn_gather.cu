@@ -9,6 +9,10 @@
 
 #include "cgnn_plan.h"
 
+#ifndef CGNN_EXPAND_RPG
+#define CGNN_EXPAND_RPG 4
+#endif
+
 namespace cgnn {
 
 static __device__ int g_gather_status = 0;
@@ -99,7 +103,9 @@ static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t
 
 template <typename T, int VW, int LPR>
 static int launch_expand(const ExpandArgs<T> &a, cudaStream_t stream) {
-    constexpr int RPG = 4;
+    // rows a lane group keeps in flight: more for narrow rows, whose single 16-byte load per lane
+    // would otherwise leave the memory pipeline short of work
+    constexpr int RPG = CGNN_EXPAND_RPG;
     const int64_t groups_needed = ceil_div(a.n, RPG);
     const int64_t per_block = 8 * (32 / LPR);
     const int64_t blocks = std::min<int64_t>(ceil_div(groups_needed, per_block), 148 * 32);

@@ -28,6 +28,7 @@ struct cgnn_plan {
     int4 *items = nullptr;         // device {long row index, first entry, end entry, 0}
     int4 *longs = nullptr;         // device {row, first item, items, first entry of the row}
     int compact = 0;               // 1: empty rows are not listed (a fresh output is cleared first)
+    void *block = nullptr;         // the one device allocation all arrays above live in
 };
 
 namespace cgnn {
@@ -35,8 +36,11 @@ namespace cgnn {
 // Build the plan's work lists and entry layout from device int32 CSR arrays of one or two
 // blocks over the same rows (p->rows, p->nterms, p->nnz set by the caller).  The inputs are
 // only read; synchronises `stream`.
+// `host_rowptr0`, when given, is a host copy of rowptr[0] the caller already has (saves a
+// device-to-host copy and a synchronisation); `want_vperm` = false skips the value permutation
+// (plans whose entries carry no values).
 int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *const col[2], int split,
-               cudaStream_t stream);
+               cudaStream_t stream, const int32_t *host_rowptr0 = nullptr, bool want_vperm = true);
 
 // Device status word of each translation unit (read-and-clear).
 int segreduce_status(int *out);

@@ -14,6 +14,7 @@
 //     ticket adds the partials in chunk order -- deterministic, no float atomics, and no
 //     unit ever waits for another.
 #include <algorithm>
+#include <cstring>
 #include <mutex>
 #include <vector>
 
@@ -508,7 +509,7 @@ __global__ void scatter_entries_kernel(const int32_t *rowptr, const int32_t *col
             const int32_t cv = col[k];
             if (cv < 0) atomicOr(&g_seg_status, STATUS_BAD_CSR);
             entries[d + (k - b)] = cv | (term ? (int32_t)0x80000000 : 0);
-            vperm[d + (k - b)] = value_base + k;
+            if (vperm) vperm[d + (k - b)] = value_base + k;
         }
     }
 }
@@ -523,32 +524,31 @@ __global__ void permute_values_kernel(const int32_t *vperm, int64_t total, int64
     }
 }
 
-template <typename V>
-static int upload(V **dev, const std::vector<V> &host) {
-    *dev = nullptr;
-    if (host.empty()) return CGNN_OK;
-    CGNN_CUDA(cudaMalloc(dev, sizeof(V) * host.size()));
-    CGNN_CUDA(cudaMemcpy(*dev, host.data(), sizeof(V) * host.size(), cudaMemcpyHostToDevice));
-    return CGNN_OK;
-}
-
 int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *const col[2], int split,
-               cudaStream_t stream) {
+               cudaStream_t stream, const int32_t *host_rowptr0, bool want_vperm) {
     const int64_t rows = p->rows;
     std::vector<int32_t> h[2];
+    const int32_t *hp[2] = {nullptr, nullptr};
+    bool copied = false;
     for (int t = 0; t < p->nterms; ++t) {
+        if (t == 0 && host_rowptr0) {
+            hp[0] = host_rowptr0;
+            continue;
+        }
         h[t].resize((size_t)rows + 1);
         CGNN_CUDA(cudaMemcpyAsync(h[t].data(), rowptr[t], sizeof(int32_t) * ((size_t)rows + 1),
                                   cudaMemcpyDeviceToHost, stream));
+        hp[t] = h[t].data();
+        copied = true;
     }
-    CGNN_CUDA(cudaStreamSynchronize(stream));
+    if (copied) CGNN_CUDA(cudaStreamSynchronize(stream));
     for (int t = 0; t < p->nterms; ++t) {
-        CGNN_REQUIRE(h[t][0] == 0, "plan: rowptr[0] must be 0 (term %d)", t);
+        CGNN_REQUIRE(hp[t][0] == 0, "plan: rowptr[0] must be 0 (term %d)", t);
         for (int64_t r = 0; r < rows; ++r)
-            CGNN_REQUIRE(h[t][r + 1] >= h[t][r], "plan: rowptr not monotone at row %lld (term %d)",
+            CGNN_REQUIRE(hp[t][r + 1] >= hp[t][r], "plan: rowptr not monotone at row %lld (term %d)",
                          (long long)r, t);
-        CGNN_REQUIRE(h[t][rows] == p->nnz[t], "plan: rowptr[rows]=%d but nnz=%lld (term %d)",
-                     h[t][rows], (long long)p->nnz[t], t);
+        CGNN_REQUIRE(hp[t][rows] == p->nnz[t], "plan: rowptr[rows]=%d but nnz=%lld (term %d)",
+                     hp[t][rows], (long long)p->nnz[t], t);
     }
     const int64_t total = p->nnz[0] + p->nnz[1];
     p->total = total;
@@ -561,8 +561,8 @@ int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *cons
     }
     p->split = split;
     auto degree = [&](int64_t r) {
-        int64_t d = h[0][r + 1] - h[0][r];
-        if (p->nterms > 1) d += h[1][r + 1] - h[1][r];
+        int64_t d = hp[0][r + 1] - hp[0][r];
+        if (p->nterms > 1) d += hp[1][r + 1] - hp[1][r];
         return d;
     };
     int64_t short_nonempty = 0, long_rows = 0;
@@ -599,34 +599,51 @@ int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *cons
     CGNN_REQUIRE(pos == total, "plan: internal entry count mismatch");
     p->n_long = (int64_t)longs.size();
     p->n_items = (int64_t)items.size();
-    int rc = upload(&p->uptr, uptr);
-    if (rc == CGNN_OK) rc = upload(&p->urow, urow);
-    if (rc == CGNN_OK) rc = upload(&p->items, items);
-    if (rc == CGNN_OK) rc = upload(&p->longs, longs);
-    if (rc != CGNN_OK || total == 0) return rc;
-    int32_t *dst_dev = nullptr;
-    rc = upload(&dst_dev, dst);
-    if (rc != CGNN_OK) return rc;
-    if (cudaMalloc(&p->entries, sizeof(int32_t) * (size_t)total) != cudaSuccess ||
-        cudaMalloc(&p->vperm, sizeof(int32_t) * (size_t)total) != cudaSuccess) {
-        cudaFree(dst_dev);
-        set_error("plan: device allocation failed");
+
+    // One device block holds every array; the small ones go up in one staged copy.
+    auto span = [](size_t bytes) { return align_up(std::max<size_t>(bytes, 16), 256); };
+    const size_t o_uptr = 0;
+    const size_t o_urow = o_uptr + span(uptr.size() * 4);
+    const size_t o_items = o_urow + span(urow.size() * 4);
+    const size_t o_longs = o_items + span(items.size() * 16);
+    const size_t o_dst = o_longs + span(longs.size() * 16);
+    const size_t staged = o_dst + span(dst.size() * 4);
+    const size_t o_entries = staged;
+    const size_t o_vperm = o_entries + span((size_t)total * 4);
+    const size_t bytes = o_vperm + (want_vperm ? span((size_t)total * 4) : 0);
+    std::vector<char> stage(staged, 0);
+    auto put = [&](size_t off, const void *src, size_t n) { if (n) std::memcpy(stage.data() + off, src, n); };
+    put(o_uptr, uptr.data(), uptr.size() * 4);
+    put(o_urow, urow.data(), urow.size() * 4);
+    put(o_items, items.data(), items.size() * 16);
+    put(o_longs, longs.data(), longs.size() * 16);
+    put(o_dst, dst.data(), dst.size() * 4);
+    if (cudaMalloc(&p->block, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        set_error("plan: device allocation of %zu bytes failed", bytes);
         return CGNN_ERR_CUDA;
     }
-    const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 8), 148 * 16));
-    for (int t = 0; t < p->nterms; ++t) {
-        if (p->nnz[t] == 0) continue;
-        scatter_entries_kernel<<<blocks, 256, 0, stream>>>(rowptr[t], col[t], dst_dev, t ? rowptr[0] : nullptr,
-                                                           rows, t, t ? (int32_t)p->nnz[0] : 0, p->entries,
-                                                           p->vperm);
+    char *base = reinterpret_cast<char *>(p->block);
+    CGNN_CUDA(cudaMemcpyAsync(base, stage.data(), staged, cudaMemcpyHostToDevice, stream));
+    p->uptr = reinterpret_cast<int32_t *>(base + o_uptr);
+    p->urow = identity ? nullptr : reinterpret_cast<int32_t *>(base + o_urow);
+    p->items = reinterpret_cast<int4 *>(base + o_items);
+    p->longs = reinterpret_cast<int4 *>(base + o_longs);
+    p->entries = reinterpret_cast<int32_t *>(base + o_entries);
+    p->vperm = want_vperm ? reinterpret_cast<int32_t *>(base + o_vperm) : nullptr;
+    const int32_t *dst_dev = reinterpret_cast<const int32_t *>(base + o_dst);
+    if (total > 0) {
+        const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 8), 148 * 16));
+        for (int t = 0; t < p->nterms; ++t) {
+            if (p->nnz[t] == 0) continue;
+            scatter_entries_kernel<<<blocks, 256, 0, stream>>>(rowptr[t], col[t], dst_dev, t ? rowptr[0] : nullptr,
+                                                               rows, t, t ? (int32_t)p->nnz[0] : 0, p->entries,
+                                                               p->vperm);
+        }
+        CGNN_LAUNCH_CHECK();
     }
-    cudaError_t e = cudaGetLastError();
-    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
-    cudaFree(dst_dev);
-    if (e != cudaSuccess) {
-        set_error("plan: entry scatter failed: %s", cudaGetErrorString(e));
-        return CGNN_ERR_CUDA;
-    }
+    // the staged host buffer must outlive the copy
+    CGNN_CUDA(cudaStreamSynchronize(stream));
     return CGNN_OK;
 }
 
@@ -756,9 +773,7 @@ int cgnn_plan_create(cgnn_plan **plan_out, int64_t rows, int index_bytes, const 
 
 void cgnn_plan_destroy(cgnn_plan *p) {
     if (!p) return;
-    void *owned[] = {p->entries, p->vperm, p->uptr, p->urow, p->items, p->longs};
-    for (void *q : owned)
-        if (q) cudaFree(q);
+    if (p->block) cudaFree(p->block);
     delete p;
 }
 
@@ -778,6 +793,7 @@ int cgnn_plan_info(const cgnn_plan *p, int64_t info[8]) {
 int cgnn_plan_permute_values(const cgnn_plan *p, int dtype, const void *val0, const void *val1,
                              void *out, cgnn_stream_t stream) {
     CGNN_REQUIRE(p != nullptr, "permute_values: null plan");
+    CGNN_REQUIRE(p->vperm != nullptr || p->total == 0, "permute_values: this plan carries no value order");
     CGNN_REQUIRE(dtype == CGNN_F32 || dtype == CGNN_F64, "permute_values: unknown dtype %d", dtype);
     if (p->total == 0) return CGNN_OK;
     CGNN_REQUIRE(out != nullptr && (val0 != nullptr || p->nnz[0] == 0) &&
