@@ -136,7 +136,7 @@ project_kernel(const T *__restrict__ x, const T *__restrict__ planes, int64_t n,
     constexpr bool PACKED = sizeof(T) == 4;
     using Acc = typename std::conditional<PACKED, float2, T>::type;
     constexpr int NACC = PACKED ? HB / 2 : HB;
-    Acc acc[RPT][NACC];
+    Acc acc[RPT][NACC] = {};
     auto plane = [&](int i, int h) -> T {
         if constexpr (PACKED) return (h & 1) ? acc[i][h >> 1].y : acc[i][h >> 1].x;
         else return acc[i][h];

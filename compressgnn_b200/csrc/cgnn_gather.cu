@@ -35,54 +35,58 @@ struct ExpandArgs {
     int64_t n, width, groups;
 };
 
-// LPR lanes own one output row at a time and walk it in steps of LPR vectors; RPG rows per
-// group are loaded before any is stored.
-template <typename T, int VW, int LPR, int RPG>
+// A group of LPR lanes expands LPR consecutive node rows per step: lane l reads index[r0 + l]
+// (one coalesced load), the indices are broadcast by shuffle, and U table rows are in flight
+// per lane before any output row is stored.
+template <typename T, int VW, int LPR, int U>
 __global__ void __launch_bounds__(256) expand_kernel(const ExpandArgs<T> a) {
     using V = Vec<T, VW>;
     constexpr int GPW = 32 / LPR;
     const int lane = threadIdx.x & 31;
     const int gl = lane & (LPR - 1);
+    const unsigned gmask = LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (lane & ~(LPR - 1)));
     const int64_t group = ((int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * GPW + lane / LPR;
     const int64_t ngroups = (int64_t)gridDim.x * (blockDim.x >> 5) * GPW;
     const int64_t vecs = a.width / VW;
-    for (int64_t r0 = group * RPG; r0 < a.n; r0 += ngroups * RPG) {
-        int64_t g[RPG];
-        T divisor[RPG];
-#pragma unroll
-        for (int i = 0; i < RPG; ++i) {
-            g[i] = -1;
-            divisor[i] = T(1);
-            if (r0 + i < a.n) {
-                const int64_t gi = a.index[r0 + i];
-                if (gi < 0 || gi >= a.groups) {
-                    if (gl == 0) atomicOr(&g_gather_status, STATUS_BAD_INDEX);
-                } else {
-                    g[i] = gi;
-                    if (a.div_counts) divisor[i] = (T)max(a.div_counts[gi], 1);
-                }
-            }
+    for (int64_t r0 = group * LPR; r0 < a.n; r0 += ngroups * LPR) {
+        int32_t gi = -1;
+        if (r0 + gl < a.n) {
+            const int64_t g = a.index[r0 + gl];
+            if (g < 0 || g >= a.groups) atomicOr(&g_gather_status, STATUS_BAD_INDEX);
+            else gi = (int32_t)g;
         }
-        for (int64_t c = gl; c < vecs; c += LPR) {
-            V x[RPG];
+        const int cnt = (int)min((int64_t)LPR, a.n - r0);
+        for (int64_t cbase = 0; cbase < vecs; cbase += LPR) {  // uniform trip count in the group
+            const int64_t c = cbase + gl;
+            const bool active = c < vecs;
             V b = vec_zero<T, VW>();
-            if (a.bias) b = vec_load<T, VW>(a.bias + c * VW);
+            if (a.bias && active) b = vec_load<T, VW>(a.bias + c * VW);
+            for (int j = 0; j < cnt; j += U) {
+                V x[U];
+                T divisor[U];
 #pragma unroll
-            for (int i = 0; i < RPG; ++i)
-                x[i] = g[i] >= 0 ? vec_load<T, VW>(a.table + g[i] * a.width + c * VW)
-                                 : vec_zero<T, VW>();
-#pragma unroll
-            for (int i = 0; i < RPG; ++i) {
-                if (r0 + i < a.n) {
-                    V y;
-#pragma unroll
-                    for (int k = 0; k < VW; ++k) {
-                        T v = x[i].v[k];
-                        if (a.bias) v += b.v[k];
-                        if (a.div_counts) v = v / divisor[i];
-                        y.v[k] = (a.relu && v < T(0)) ? T(0) : v;
+                for (int u = 0; u < U; ++u) {
+                    const int32_t g = __shfl_sync(gmask, gi, j + u, LPR);
+                    x[u] = vec_zero<T, VW>();
+                    divisor[u] = T(1);
+                    if (active && j + u < cnt && g >= 0) {
+                        x[u] = vec_load<T, VW>(a.table + (int64_t)g * a.width + c * VW);
+                        if (a.div_counts) divisor[u] = (T)max(a.div_counts[g], 1);
                     }
-                    vec_store_cs<T, VW>(a.out + (r0 + i) * a.width + c * VW, y);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (active && j + u < cnt) {
+                        V y;
+#pragma unroll
+                        for (int k = 0; k < VW; ++k) {
+                            T v = x[u].v[k];
+                            if (a.bias) v += b.v[k];
+                            if (a.div_counts) v = v / divisor[u];
+                            y.v[k] = (a.relu && v < T(0)) ? T(0) : v;
+                        }
+                        vec_store_cs<T, VW>(a.out + (r0 + j + u) * a.width + c * VW, y);
+                    }
                 }
             }
         }
@@ -103,13 +107,11 @@ static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t
 
 template <typename T, int VW, int LPR>
 static int launch_expand(const ExpandArgs<T> &a, cudaStream_t stream) {
-    // rows a lane group keeps in flight: more for narrow rows, whose single 16-byte load per lane
-    // would otherwise leave the memory pipeline short of work
-    constexpr int RPG = CGNN_EXPAND_RPG;
-    const int64_t groups_needed = ceil_div(a.n, RPG);
+    constexpr int U = CGNN_EXPAND_RPG;  // table rows in flight per lane
+    const int64_t groups_needed = ceil_div(a.n, LPR);
     const int64_t per_block = 8 * (32 / LPR);
     const int64_t blocks = std::min<int64_t>(ceil_div(groups_needed, per_block), 148 * 32);
-    expand_kernel<T, VW, LPR, RPG><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    expand_kernel<T, VW, LPR, U><<<(unsigned)blocks, 256, 0, stream>>>(a);
     CGNN_LAUNCH_CHECK();
     return CGNN_OK;
 }

@@ -29,6 +29,8 @@ struct cgnn_plan {
     int4 *longs = nullptr;         // device {row, first item, items, first entry of the row}
     int compact = 0;               // 1: empty rows are not listed (a fresh output is cleared first)
     void *block = nullptr;         // the one device allocation all arrays above live in
+    cudaStream_t home = nullptr;   // stream the block was allocated on (stream-ordered allocator)
+    bool pooled = false;           // block came from cudaMallocAsync
 };
 
 namespace cgnn {

@@ -618,10 +618,18 @@ int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *cons
     put(o_items, items.data(), items.size() * 16);
     put(o_longs, longs.data(), longs.size() * 16);
     put(o_dst, dst.data(), dst.size() * 4);
-    if (cudaMalloc(&p->block, bytes) != cudaSuccess) {
+    // Stream-ordered allocation: an assignment refresh builds and drops a plan every few epochs,
+    // and cudaMalloc / cudaFree would each stall the whole device.
+    p->home = stream;
+    p->pooled = cudaMallocAsync(&p->block, bytes, stream) == cudaSuccess;
+    if (!p->pooled) {
         cudaGetLastError();
-        set_error("plan: device allocation of %zu bytes failed", bytes);
-        return CGNN_ERR_CUDA;
+        if (cudaMalloc(&p->block, bytes) != cudaSuccess) {
+            cudaGetLastError();
+            p->block = nullptr;
+            set_error("plan: device allocation of %zu bytes failed", bytes);
+            return CGNN_ERR_CUDA;
+        }
     }
     char *base = reinterpret_cast<char *>(p->block);
     CGNN_CUDA(cudaMemcpyAsync(base, stage.data(), staged, cudaMemcpyHostToDevice, stream));
@@ -773,7 +781,14 @@ int cgnn_plan_create(cgnn_plan **plan_out, int64_t rows, int index_bytes, const 
 
 void cgnn_plan_destroy(cgnn_plan *p) {
     if (!p) return;
-    if (p->block) cudaFree(p->block);
+    if (p->block) {
+        // released in the order of the stream the plan was built on; a launch that still uses
+        // the plan on ANOTHER stream must have been waited for by the caller
+        if (!p->pooled || cudaFreeAsync(p->block, p->home) != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(p->block);
+        }
+    }
     delete p;
 }
 

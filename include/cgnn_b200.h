@@ -59,6 +59,8 @@ int cgnn_plan_create(cgnn_plan **plan_out, int64_t rows, int index_bytes,
 int cgnn_plan_create_from_index(cgnn_plan **plan_out, const int64_t *index, int64_t n,
                                 int64_t groups, int split, cgnn_stream_t stream);
 
+/* Plan memory is released in the order of the stream the plan was created on; do not destroy
+ * a plan while a launch that uses it may still run on a different stream. */
 void cgnn_plan_destroy(cgnn_plan *plan);
 
 /* info[0..7] = rows, entries (both terms), split, long rows, chunks, rows in the direct

@@ -185,3 +185,32 @@ def test_golden_propagation_through_spmm_func(rt, golden):
     gx = rt.spmm_func(*tr(blocks["v2v"], n), g, "rowbalance_rowcache", None)
     gx = rt.spmm_func(*tr(blocks["r2v"], n), rule_g, "rowbalance_rowcache", gx)
     assert_close_rel(gx.cpu().numpy(), golden["dag_backward"], what="golden backward")
+
+
+def test_offsets_beyond_32_bits(rt):
+    """Source matrices with more than 2^31 elements (the 18.5 M-node x 128 configuration): row
+    offsets are 64-bit in every kernel (the reference's rowcache kernel multiplies in int32)."""
+    free, _total = torch.cuda.mem_get_info()
+    src_rows, width = 17_500_000, 128  # 2.24e9 elements, 8.96 GB
+    if free < 12 * 2**30:
+        pytest.skip("needs 12 GB of free device memory")
+    x = torch.zeros(src_rows, width, device="cuda")
+    rng = np.random.default_rng(31)
+    picks = np.unique(np.concatenate([rng.integers(16_900_000, src_rows, 200), [src_rows - 1, 16_777_216]]))
+    x[torch.from_numpy(picks).cuda()] = torch.randn(picks.size, width, device="cuda")
+    rows = 64
+    deg = rng.integers(1, 9, rows)
+    deg[5] = 150  # a chunked row as well
+    rowptr = np.zeros(rows + 1, np.int64)
+    rowptr[1:] = np.cumsum(deg)
+    col = rng.choice(picks, rowptr[-1]).astype(np.int64)
+    val = rng.standard_normal(col.size).astype(np.float32)
+    out = rt.spmm_func(cu(rowptr), cu(col), cu(val), x, "rowbalance_rowcache", None)
+    sub = x[torch.from_numpy(col).cuda()].cpu().numpy().astype(np.float64) * val[:, None]
+    ref = np.add.reduceat(sub, rowptr[:-1], axis=0)
+    assert_close_rel(out.cpu().numpy(), ref, what="rows beyond 2^31 elements")
+    idx = torch.from_numpy(rng.choice(picks, 1000)).cuda()
+    y = rt.cluster_reconstruct(x, idx, None, False)
+    assert torch.equal(y, x.index_select(0, idx))
+    del x
+    torch.cuda.empty_cache()
