@@ -43,6 +43,9 @@ WORKLOADS = {
     "propagation-xl": dict(n=18500000, x_min=8.6, width=128, seed=4),
 }
 COMPRESS = dict(min_pair_frequency=4, threshold=4, max_depth=3, min_edge=1000000)
+# dram__bytes_read.sum + dram__bytes_write.sum of one forward fused vertex pass at N=1, from the
+# ncu capture summarised in profiles/seg_kernel_fused_vertex_pass_config2.md (same workload).
+NCU_TRAFFIC_BYTES = {("propagation", 1): 1.444e9}
 
 
 def build_graph(name):
@@ -333,7 +336,7 @@ def run_gpu(args):
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "kernel": "seg_kernel (fused v2r+v2v vertex pass, forward)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_source": peak_src, "traffic": None,
+                     "peak_source": peak_src, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, world)),
                      "algorithmic_bytes_per_launch": bytes_by_name[dom], "ms_per_launch": launch_ms[dom],
                      "launches": {k: {"ms": launch_ms[k], "algorithmic_GBps": bytes_by_name[k] / launch_ms[k] / 1e6}
                                   for k in launch_ms}},
