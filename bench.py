@@ -9,6 +9,10 @@ on a seeded copying-model web graph with 325,557 nodes and ~3.2 M edges, feature
 One step = one forward and one backward pass over the whole graph.  The metric is
 original-edge x feature products per second: 2 * E_orig * F / t_step.
 
+With N GPUs the feature columns are sharded and the graph replicated (no data-path collective).
+The default is weak scaling -- each GPU keeps a 256-column block, so the job's matrix is
+N x 256*gpus; `--scaling strong` divides the 256 columns instead.
+
 Prints ONE JSON line (rank 0).  `value` is device-resident throughput (CUDA events, max over
 ranks); `e2e` goes through the public module API with pinned host buffers, copies included;
 `roofline` is for the dominant kernel (the fused vertex pass of the forward); `cpu_baseline`
@@ -213,9 +217,14 @@ def run_gpu(args):
         dist.init_process_group("nccl", device_id=device)
 
     wl = WORKLOADS[args.workload]
-    width_total = wl["width"]
-    assert width_total % world == 0, "feature width must divide by the number of GPUs"
-    width = width_total // world  # column shard of this rank; the graph is replicated
+    if args.scaling == "weak":
+        # every rank holds a full-width column block: the job's feature matrix is N x (F * world)
+        width = wl["width"]
+        width_total = width * world
+    else:
+        width_total = wl["width"]
+        assert width_total % world == 0, "feature width must divide by the number of GPUs"
+        width = width_total // world  # column shard of this rank; the graph is replicated
     data, e_orig = build_graph(args.workload)
     cpu_graph_for_baseline = data if rank == 0 else None
     graph = data.edge_index
@@ -324,7 +333,7 @@ def run_gpu(args):
     line = {
         "metric": METRIC, "value": work / (ms_per_step * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{args.workload}: compressed propagation SpMM fwd+bwd, copying-model web graph",
                    "nodes": n, "orig_edges": e_orig, "compressed_edges": graph.edge_count(),
                    "rules": graph.rule_cnt, "levels": graph.step, "feature_width": width_total,
@@ -454,17 +463,25 @@ def run_reference(args):
     if rank != 0:
         return
     wl = WORKLOADS[args.workload]
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     data, e_orig = build_graph(args.workload)
+    # The CPU has no GPUs to scale over: it runs one 256-column block per step whatever N is; in the
+    # weak-scaling configuration (N blocks) the time per step is N times that, the throughput the same.
     sec, kind, cores, sample = cpu_propagation(data, wl["width"], args.steps, min(args.warmup, 2))
-    value = 2 * e_orig * wl["width"] / sec / 1e9
+    blocks = world if args.scaling == "weak" else 1
+    if blocks > 1:
+        sample += f"; one of {blocks} column blocks timed, step time scaled by {blocks}"
+    total_width = wl["width"] * blocks
+    sec *= blocks
+    value = 2 * e_orig * total_width / sec / 1e9
     g = data.edge_index
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
         "steps": args.steps, "warmup": min(args.warmup, 2), "ms_per_step": sec * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"{args.workload}: compressed propagation SpMM fwd+bwd, copying-model web graph",
                    "nodes": g.vertex_cnt, "orig_edges": e_orig, "compressed_edges": g.edge_count(),
-                   "rules": g.rule_cnt, "levels": g.step, "feature_width": wl["width"], "compressor": COMPRESS},
+                   "rules": g.rule_cnt, "levels": g.step, "feature_width": total_width, "compressor": COMPRESS},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -480,6 +497,9 @@ def main():
     ap.add_argument("--impl", choices=["cgnn", "reference"], default="cgnn")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cluster"], default="propagation")
     ap.add_argument("--cluster-nodes", type=int, default=2450000)
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                    help="weak: every GPU holds a full-width (256-column) block of a feature matrix that is "
+                         "N x 256*gpus; strong: the 256 columns are divided among the GPUs")
     ap.add_argument("--cpu-steps", type=int, default=3, help="steps of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
