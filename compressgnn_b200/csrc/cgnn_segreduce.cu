@@ -226,12 +226,15 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kern
     const int64_t direct_units = (a.n_direct + RPU - 1) / RPU;
 
     int e_begin, e_end, nr = 0, myptr = 0;
+    int32_t myrow = 0;  // row id of listed row `gl` of this unit (fetched up front: a load at
+                        // flush time would stall the store that needs it as its address)
     int64_t first = 0;
     int64_t item_index = -1;
     if (unit < direct_units) {
         first = unit * RPU;
         nr = (int)min((int64_t)RPU, a.n_direct - first);
         if (gl <= nr) myptr = a.uptr[first + gl];
+        if (gl < nr) myrow = a.urow ? a.urow[first + gl] : (int32_t)(first + gl);
         e_begin = __shfl_sync(gmask, myptr, 0, LPR);
         e_end = __shfl_sync(gmask, myptr, nr, LPR);
     } else {
@@ -247,7 +250,7 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kern
     int row_begin = e_begin;  // its entry range
     int row_end = item_index >= 0 ? e_end : __shfl_sync(gmask, myptr, 1, LPR);
     auto flush = [&]() {  // finish listed row `cur` and move to the next one
-        const int32_t row = a.urow ? a.urow[first + cur] : (int32_t)(first + cur);
+        const int32_t row = __shfl_sync(gmask, myrow, cur, LPR);
         finish_row<T, VW, LPR, VPL>(a, row, row_begin < row_end ? row_begin : -1, acc, colbase, colok);
 #pragma unroll
         for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
