@@ -358,6 +358,51 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def cpu_cluster(n, width, out_width, bits, fraction=8):
+    """The reference's CPU path of the same epoch on 1/`fraction` of the nodes (all host threads):
+    cluster_forward (src/runtime/csrc/cluster/cpu/cluster_cpu.cpp:27-70) + bincount, the mean and its
+    backward as layer/CompressgnnCluster.py:16-25 computes them, Linear, and the CPU reconstruct of
+    layer/CompressgnnReconstruct.py:39-42 with autograd for its backward."""
+    import torch
+    from oracle import oracle
+    rt, _off = oracle.reference_modules()
+    if rt is None:
+        return {"value": None, "unit": "Mnode/s", "cores": 0, "kind": "reference",
+                "sample": "unavailable: oracle/_ref is not built on this box"}
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    m = n // fraction
+    gen = torch.Generator().manual_seed(3)
+    cent = torch.randn(4096, width, generator=gen)
+    x = (cent[torch.randint(0, 4096, (m,), generator=gen)] + 0.1 * torch.randn(m, width, generator=gen)).requires_grad_()
+    planes = torch.randn(width, bits, generator=gen)
+    lin = torch.nn.Linear(width, out_width)
+    grad_out = torch.randn(m, out_width, generator=gen)
+
+    def epoch(refresh, state):
+        if refresh:
+            ids, active = rt.cluster_forward(x.detach(), planes, bits)
+            index = ids.long()
+            state["index"], state["counts"] = index, torch.bincount(index, minlength=active + 1)
+        index, counts = state["index"], state["counts"]
+        sums = torch.zeros(counts.numel(), width).index_add_(0, index, x)
+        reps = sums / counts.clamp_min(1).to(torch.float32)[:, None]
+        y = (torch.nn.functional.linear(reps, lin.weight, None).index_select(0, index) + lin.bias).relu()
+        y.backward(grad_out)
+        x.grad = None
+
+    state = {}
+    epoch(True, state)
+    t0 = time.perf_counter()
+    epochs = 5
+    for e in range(epochs):
+        epoch(e % 5 == 0, state)
+    sec = (time.perf_counter() - t0) / epochs * fraction
+    return {"value": n / sec / 1e6, "unit": "Mnode/s", "cores": cores, "kind": "reference",
+            "ms_per_step": sec * 1e3,
+            "sample": f"{m} of {n} nodes, {epochs} epochs with one refresh, time scaled by {fraction}"}
+
+
 def run_cluster(args):
     """Config 3: Compressgnn_Cluster -> Linear(128->256) on representatives -> fused reconstruct
     (bias + ReLU), forward + backward, 2.45 M nodes drawn from 4096 Gaussian centroids, H=16,
@@ -445,6 +490,7 @@ def run_cluster(args):
         ms = timed(fn)
         op_report[name] = {"ms": ms, "algorithmic_GBps": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / peak}
     assert rt.device_status() == 0
+    cpu = None if args.no_cpu_baseline else cpu_cluster(n, width, out_width, bits)
     line = {"metric": "cluster_linear_reconstruct_nodes_per_s", "value": n / (ms_epoch * 1e-3) / 1e6, "unit": "Mnode/s",
             "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_epoch,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -454,6 +500,63 @@ def run_cluster(args):
                        "l2": "inputs larger than L2 (X is %.0f MB)" % (4e-6 * n * width)},
             "operators": op_report, "peak_GBps": peak, "clocks": clocks.summary(),
             "gpu_launches": None}
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line))
+
+
+def run_gcn(args):
+    """Config 5: end-to-end 2-layer GCN with propagation and transformation compression
+    (use_transformation=True, H=16, refresh_interval=5) on the config-2 graph, 47 uniform classes,
+    input feature width swept over 16/64/256/1024.  A step = one training epoch (forward, NLL loss
+    on all nodes, backward, Adam step), timed after warm-up epochs as the reference's
+    benchmark/end2end/compressgnn_gcn.py does."""
+    import torch
+    from compressgnn_b200.model import GCN
+    torch.cuda.set_device(0)
+    data, e_orig = build_graph("propagation")
+    graph = data.edge_index
+    n = graph.vertex_cnt
+    graph.to("cuda")
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    y = torch.randint(0, 47, (n,), device="cuda", generator=gen)
+    report = {}
+    for width in (16, 64, 256, 1024):
+        x = torch.randn(n, width, device="cuda", generator=gen)
+        torch.manual_seed(5)
+        model = GCN(width, 47, hidden_features=128, param_H=16, dropout=0.3, use_transformation=True,
+                    refresh_interval=5, num_layers=2).cuda()
+        opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+
+        def epoch(e):
+            model.set_epoch(e)
+            opt.zero_grad(set_to_none=True)
+            loss = torch.nn.functional.nll_loss(model(x, graph), y)
+            loss.backward()
+            opt.step()
+            return loss
+
+        for e in range(max(args.warmup, 3)):
+            epoch(e)
+        model.reset_cache()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for e in range(args.steps):
+            loss = epoch(e)
+        stop.record()
+        torch.cuda.synchronize()
+        report[str(width)] = {"epoch_ms": start.elapsed_time(stop) / args.steps, "final_loss": float(loss)}
+        del model, opt, x
+    from compressgnn_b200 import runtime as rt
+    assert rt.device_status() == 0
+    line = {"metric": "gcn_epoch_ms", "value": report["256"]["epoch_ms"], "unit": "ms", "n_gpus": 1,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": report["256"]["epoch_ms"],
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "gcn: 2-layer GCN, propagation + transformation compression, config-2 graph",
+                       "nodes": n, "orig_edges": e_orig, "rules": graph.rule_cnt, "levels": graph.step, "classes": 47,
+                       "hidden": 128, "bits": 16, "refresh_interval": 5, "compressor": COMPRESS},
+            "epoch_ms_by_feature_width": report, "gpu_launches": None}
     print(json.dumps(line))
 
 
@@ -495,7 +598,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["cgnn", "reference"], default="cgnn")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cluster"], default="propagation")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cluster", "gcn"], default="propagation")
     ap.add_argument("--cluster-nodes", type=int, default=2450000)
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="weak: every GPU holds a full-width (256-column) block of a feature matrix that is "
@@ -505,6 +608,8 @@ def main():
     args = ap.parse_args()
     if args.workload == "cluster":
         run_cluster(args)
+    elif args.workload == "gcn":
+        run_gcn(args)
     elif args.impl == "reference":
         run_reference(args)
     else:
