@@ -14,9 +14,10 @@
 #include <cstdio>
 #include <cstring>
 #include <numeric>
+#include <omp.h>
+#include <parallel/algorithm>
 #include <random>
 #include <string>
-#include <unordered_map>
 #include <vector>
 
 #define CGNN_HOST_API extern "C" __attribute__((visibility("default")))
@@ -129,15 +130,6 @@ int rule_depths(const int64_t *vlist, const int64_t *elist, int64_t n, int64_t r
     }
     return step - 1;
 }
-
-struct PairHash {
-    size_t operator()(uint64_t k) const {
-        k ^= k >> 33;
-        k *= 0xff51afd7ed558ccdULL;
-        k ^= k >> 33;
-        return (size_t)k;
-    }
-};
 
 }  // namespace
 
@@ -260,7 +252,6 @@ CGNN_HOST_API int cgnn_host_transpose_csr(const int64_t *vlist, const int64_t *e
 CGNN_HOST_API int cgnn_host_compress_csr_batch(const int64_t *vlist, const int64_t *elist, int64_t n,
                                                int threads, int rounds, int min_frequency,
                                                Result **out) {
-    (void)threads;
     if (min_frequency < 3) return fail("Batch compression needs min_pair_frequency >= 3");
     if (rounds < 1) return fail("compression_rounds must be positive");
     const int64_t edges = n > 0 ? vlist[n] : 0;
@@ -274,78 +265,108 @@ CGNN_HOST_API int cgnn_host_compress_csr_batch(const int64_t *vlist, const int64
         }
     }
     std::vector<std::pair<int32_t, int32_t>> rules;
-    std::vector<int32_t> tmp;
+    if (threads > 0) omp_set_num_threads(threads);
+    std::vector<uint64_t> keys;      // every adjacent pair of every row, then sorted
+    std::vector<uint64_t> cand_key;  // pairs seen often enough, ascending
+    std::vector<int32_t> cand_count;
+    std::vector<int64_t> offset((size_t)n + 1);
     for (int round = 0; round < rounds; ++round) {
-        std::unordered_map<uint64_t, int32_t, PairHash> count;
-        count.reserve((size_t)edges / 2 + 16);
-        for (const auto &row : rows)
-            for (size_t i = 0; i + 1 < row.size(); ++i)
-                ++count[((uint64_t)(uint32_t)row[i] << 32) | (uint32_t)row[i + 1]];
-        std::vector<uint64_t> keys;
-        for (const auto &kv : count)
-            if (kv.second >= min_frequency) keys.push_back(kv.first);
+        // 1. all adjacent pairs, gathered in parallel and sorted: counting is a run-length pass
+        offset[0] = 0;
+        for (int64_t v = 0; v < n; ++v)
+            offset[v + 1] = offset[v] + (rows[v].size() > 1 ? (int64_t)rows[v].size() - 1 : 0);
+        keys.resize((size_t)offset[n]);
         if (keys.empty()) break;
-        std::sort(keys.begin(), keys.end());
-        const int64_t base = n + (int64_t)rules.size();
-        if (base + (int64_t)keys.size() >= INT32_MAX) return fail("rule ids exceed int32 capacity");
-        std::unordered_map<uint64_t, int32_t, PairHash> rule_of;
-        rule_of.reserve(keys.size() * 2);
-        for (size_t k = 0; k < keys.size(); ++k) rule_of[keys[k]] = (int32_t)(base + (int64_t)k);
-        std::vector<int32_t> uses(keys.size(), 0);
-        std::vector<int32_t> rid;      // candidate rule at each position of the row, or -1
-        std::vector<uint64_t> weight;  // (pair count, rule id): the parse prefers heavier pairs
-        for (auto &row : rows) {
-            if (row.size() < 2) continue;
-            const size_t m = row.size() - 1;
-            rid.assign(m, -1);
-            weight.assign(m, 0);
-            bool any = false;
-            for (size_t i = 0; i < m; ++i) {
-                const uint64_t key = ((uint64_t)(uint32_t)row[i] << 32) | (uint32_t)row[i + 1];
-                auto it = rule_of.find(key);
-                if (it != rule_of.end()) {
-                    rid[i] = it->second;
-                    weight[i] = ((uint64_t)(uint32_t)count[key] << 32) | (uint32_t)it->second;
-                    any = true;
-                }
-            }
-            if (!any) continue;
-            // A pair is substituted where it outweighs both overlapping neighbours, so rows
-            // that share a run of symbols parse it the same way wherever the run starts; what
-            // this leaves is then taken greedily from the left.
-            tmp.clear();
-            std::vector<char> take(m, 0);
-            for (size_t i = 0; i < m; ++i)
-                if (rid[i] >= 0 && (i == 0 || weight[i] > weight[i - 1]) &&
-                    (i + 1 == m || weight[i] >= weight[i + 1]))
-                    take[i] = 1;
-            for (size_t i = 0; i < m; ++i)
-                if (!take[i] && rid[i] >= 0 && (i == 0 || !take[i - 1]) && (i + 1 == m || !take[i + 1]))
-                    take[i] = 1;
-            size_t i = 0;
-            while (i < row.size()) {
-                if (i < m && take[i]) {
-                    tmp.push_back(rid[i]);
-                    ++uses[(size_t)(rid[i] - base)];
-                    i += 2;
-                } else {
-                    tmp.push_back(row[i++]);
-                }
-            }
-            row.assign(tmp.begin(), tmp.end());
+#pragma omp parallel for schedule(static)
+        for (int64_t v = 0; v < n; ++v) {
+            const auto &row = rows[v];
+            uint64_t *dst = keys.data() + offset[v];
+            for (size_t i = 0; i + 1 < row.size(); ++i)
+                dst[i] = ((uint64_t)(uint32_t)row[i] << 32) | (uint32_t)row[i + 1];
         }
-        // Drop rules the greedy rewrite never used and close the gaps in the numbering.
-        std::vector<int32_t> remap(keys.size(), -1);
+        __gnu_parallel::sort(keys.begin(), keys.end());
+        cand_key.clear();
+        cand_count.clear();
+        for (size_t i = 0; i < keys.size();) {
+            size_t j = i + 1;
+            while (j < keys.size() && keys[j] == keys[i]) ++j;
+            if ((int64_t)(j - i) >= min_frequency) {
+                cand_key.push_back(keys[i]);
+                cand_count.push_back((int32_t)std::min<size_t>(j - i, INT32_MAX));
+            }
+            i = j;
+        }
+        if (cand_key.empty()) break;
+        const int64_t base = n + (int64_t)rules.size();
+        if (base + (int64_t)cand_key.size() >= INT32_MAX) return fail("rule ids exceed int32 capacity");
+        // rule id of a pair = base + its rank among the candidates (ascending key): deterministic
+        auto find = [&](uint64_t key) -> int64_t {
+            auto it = std::lower_bound(cand_key.begin(), cand_key.end(), key);
+            return (it != cand_key.end() && *it == key) ? (int64_t)(it - cand_key.begin()) : -1;
+        };
+        std::vector<int32_t> uses(cand_key.size(), 0);
+#pragma omp parallel
+        {
+            std::vector<int32_t> rid, tmp;  // candidate rule at each position of the row, or -1
+            std::vector<uint64_t> weight;   // (pair count, rule id): the parse prefers heavier pairs
+            std::vector<char> take;
+#pragma omp for schedule(dynamic, 1024)
+            for (int64_t v = 0; v < n; ++v) {
+                auto &row = rows[v];
+                if (row.size() < 2) continue;
+                const size_t m = row.size() - 1;
+                rid.assign(m, -1);
+                weight.assign(m, 0);
+                bool any = false;
+                for (size_t i = 0; i < m; ++i) {
+                    const int64_t k = find(((uint64_t)(uint32_t)row[i] << 32) | (uint32_t)row[i + 1]);
+                    if (k >= 0) {
+                        rid[i] = (int32_t)(base + k);
+                        weight[i] = ((uint64_t)(uint32_t)cand_count[(size_t)k] << 32) | (uint32_t)rid[i];
+                        any = true;
+                    }
+                }
+                if (!any) continue;
+                // A pair is substituted where it outweighs both overlapping neighbours, so rows
+                // that share a run of symbols parse it the same way wherever the run starts;
+                // what this leaves is then taken greedily from the left.
+                take.assign(m, 0);
+                for (size_t i = 0; i < m; ++i)
+                    if (rid[i] >= 0 && (i == 0 || weight[i] > weight[i - 1]) &&
+                        (i + 1 == m || weight[i] >= weight[i + 1]))
+                        take[i] = 1;
+                for (size_t i = 0; i < m; ++i)
+                    if (!take[i] && rid[i] >= 0 && (i == 0 || !take[i - 1]) && (i + 1 == m || !take[i + 1]))
+                        take[i] = 1;
+                tmp.clear();
+                size_t i = 0;
+                while (i < row.size()) {
+                    if (i < m && take[i]) {
+                        tmp.push_back(rid[i]);
+#pragma omp atomic
+                        ++uses[(size_t)(rid[i] - base)];
+                        i += 2;
+                    } else {
+                        tmp.push_back(row[i++]);
+                    }
+                }
+                row.assign(tmp.begin(), tmp.end());
+            }
+        }
+        // Drop rules the parse never used and close the gaps in the numbering.
+        std::vector<int32_t> remap(cand_key.size(), -1);
         int32_t next = (int32_t)base;
-        for (size_t k = 0; k < keys.size(); ++k)
+        for (size_t k = 0; k < cand_key.size(); ++k)
             if (uses[k] > 0) {
                 remap[k] = next++;
-                rules.emplace_back((int32_t)(keys[k] >> 32), (int32_t)(keys[k] & 0xffffffffu));
+                rules.emplace_back((int32_t)(cand_key[k] >> 32), (int32_t)(cand_key[k] & 0xffffffffu));
             }
-        if (next != (int32_t)(base + (int64_t)keys.size()))
-            for (auto &row : rows)
-                for (auto &s : row)
-                    if (s >= base) s = remap[(size_t)(s - base)];
+        if (next != (int32_t)(base + (int64_t)cand_key.size())) {
+#pragma omp parallel for schedule(static)
+            for (int64_t v = 0; v < n; ++v)
+                for (auto &sym : rows[v])
+                    if (sym >= base) sym = remap[(size_t)(sym - base)];
+        }
     }
     auto *res = new Result();
     std::vector<int64_t> vl{0}, el;
