@@ -30,6 +30,9 @@
 #ifndef CGNN_SEG_RPU
 #define CGNN_SEG_RPU 8      // rows per direct work unit (capped by the lane-group width)
 #endif
+#ifndef CGNN_SEG_NARROW
+#define CGNN_SEG_NARROW 1   // side-by-side lane groups for rows of at most 16 vectors
+#endif
 #ifndef CGNN_SEG_PREFETCH
 #define CGNN_SEG_PREFETCH 1    // request the next (source,value) batch before consuming the current
 #endif
@@ -341,6 +344,176 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kern
     finish_row<T, VW, LPR, VPL>(a, lr.x, lr.w, acc, colbase, colok);
 }
 
+// ---------------------------------------------------------------------------------------
+// Narrow rows (at most 16 vectors wide, i.e. F <= 64 in fp32): a feature row needs only LPR < 32
+// lanes, so a warp works on ONE work unit with its 32/LPR lane groups side by side -- group k
+// takes entries k, k+G, k+2G, ... of the unit's stream.  All groups follow the same loop (no
+// divergence between them, one coalesced entry load per 32 entries for the whole warp); each
+// keeps a partial sum of the current row, and a row is finished by adding the groups' partial
+// sums with a fixed shuffle tree.
+// ---------------------------------------------------------------------------------------
+#ifndef CGNN_SEG_NARROW_RPU
+#define CGNN_SEG_NARROW_RPU 16
+#endif
+
+template <typename T, int VW, int LPR>
+__global__ void __launch_bounds__(CGNN_SEG_THREADS) seg_narrow_kernel(const SegArgs<T> a) {
+    using V = Vec<T, VW>;
+    constexpr int G = 32 / LPR;
+    constexpr int U = 8;  // steps (G entries each) in flight per lane
+    constexpr int RPU = CGNN_SEG_NARROW_RPU;
+    constexpr unsigned FULL = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    const int gl = lane & (LPR - 1);
+    const int gk = lane / LPR;
+    const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t width = a.width;
+    const int64_t colbase = (int64_t)blockIdx.y * (LPR * VW) + gl * VW;
+    bool colok[1] = {colbase < width};
+    V acc[1] = {vec_zero<T, VW>()};
+    const int64_t direct_units = (a.n_direct + RPU - 1) / RPU;
+
+    int e_begin, e_end, nr = 0, myptr = 0;
+    int32_t myrow = 0;
+    int64_t item_index = -1;
+    if (unit < direct_units) {
+        const int64_t first = unit * RPU;
+        nr = (int)min((int64_t)RPU, a.n_direct - first);
+        if (lane <= nr) myptr = a.uptr[first + lane];
+        if (lane < nr) myrow = a.urow ? a.urow[first + lane] : (int32_t)(first + lane);
+        e_begin = __shfl_sync(FULL, myptr, 0);
+        e_end = __shfl_sync(FULL, myptr, nr);
+    } else {
+        item_index = unit - direct_units;
+        if (item_index >= a.n_items) return;  // whole warp
+        const int4 item = a.items[item_index];
+        e_begin = item.y;
+        e_end = item.z;
+    }
+    int cur = 0;
+    int row_begin = e_begin;
+    int row_end = item_index >= 0 ? e_end : __shfl_sync(FULL, myptr, 1);
+
+    // sum of the groups' partial sums, same value in every group (fixed tree)
+    auto reduce_groups = [&]() {
+        V t = acc[0];
+#pragma unroll
+        for (int m = LPR; m < 32; m <<= 1) {
+#pragma unroll
+            for (int i = 0; i < VW; ++i) t.v[i] += __shfl_xor_sync(FULL, t.v[i], m);
+        }
+        return t;
+    };
+    auto flush = [&]() {  // finish listed row `cur` and move to the next one
+        V t[1] = {reduce_groups()};
+        const int32_t row = __shfl_sync(FULL, myrow, cur);
+        if (gk == 0) finish_row<T, VW, LPR, 1>(a, row, row_begin < row_end ? row_begin : -1, t, colbase, colok);
+        acc[0] = vec_zero<T, VW>();
+        ++cur;
+        row_begin = row_end;
+        row_end = __shfl_sync(FULL, myptr, (cur + 1) & 31);
+    };
+
+    int32_t o = 0, o_next = 0;
+    T v = T(0), v_next = T(0);
+    if (e_begin + lane < e_end) {
+        o = entry_row(a, a.entries[e_begin + lane]);
+        v = a.val ? a.val[e_begin + lane] : T(1);
+    }
+    for (int base = e_begin; base < e_end; base += 32) {
+        const int nxt = base + 32 + lane;
+        if (nxt < e_end) {
+            o_next = entry_row(a, a.entries[nxt]);
+            v_next = a.val ? a.val[nxt] : T(1);
+        }
+        const int cnt = min(32, e_end - base);
+        const int steps = (cnt + G - 1) / G;
+        for (int s0 = 0; s0 < steps; s0 += U) {
+            V x[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int j = (s0 + u) * G + gk;
+                const int32_t oj = __shfl_sync(FULL, o, j & 31);
+                if (j < cnt && colok[0]) x[u] = gather_load<T, VW>(a.src0 + (int64_t)oj * width + colbase);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int s = s0 + u;
+                const int j = s * G + gk;
+                const T w = __shfl_sync(FULL, v, j & 31);
+                if (s < steps) {  // uniform
+                    const int step_first = base + s * G;
+                    const int step_last = min(step_first + G, base + cnt);
+                    const int e = base + j;
+                    if (step_last <= row_end) {  // the whole step belongs to the current row
+                        if (j < cnt && colok[0]) {
+#pragma unroll
+                            for (int i = 0; i < VW; ++i) acc[0].v[i] = fma(x[u].v[i], w, acc[0].v[i]);
+                        }
+                    } else {  // one or more rows end inside this step
+                        int lo = step_first;
+                        while (true) {
+                            const int hi = min(row_end, step_last);
+                            if (e >= lo && e < hi && colok[0]) {
+#pragma unroll
+                                for (int i = 0; i < VW; ++i) acc[0].v[i] = fma(x[u].v[i], w, acc[0].v[i]);
+                            }
+                            if (row_end > step_last) break;  // the current row goes on in the next step
+                            flush();
+                            lo = hi;
+                            if (cur >= nr) break;
+                        }
+                    }
+                }
+            }
+        }
+        o = o_next;
+        v = v_next;
+    }
+    if (item_index < 0) {
+        while (cur < nr) flush();
+        return;
+    }
+
+    // ---- chunk of a long row: group 0 publishes the partial sum and draws the ticket -------
+    V total[1] = {reduce_groups()};
+    if (gk != 0) return;
+    const unsigned gmask = (1u << LPR) - 1u;
+    const int4 item = a.items[item_index];
+    const int4 lr = a.longs[item.x];
+    T *part = a.partial + item_index * width + colbase;
+    if (colok[0]) vec_store<T, VW>(part, total[0]);
+    __threadfence();
+    __syncwarp(gmask);
+    int *tk = a.tickets + (int64_t)item.x * gridDim.y + blockIdx.y;
+    int ticket = 0;
+    if (gl == 0) ticket = atomicAdd(tk, 1);
+    ticket = __shfl_sync(gmask, ticket, 0, LPR);
+    if (ticket != lr.z - 1) return;
+    __threadfence();
+    total[0] = vec_zero<T, VW>();
+    for (int s = 0; s < lr.z; ++s) {
+        if (colok[0]) {
+            const V q = vec_load_cg<T, VW>(a.partial + (int64_t)(lr.y + s) * width + colbase);
+#pragma unroll
+            for (int i = 0; i < VW; ++i) total[0].v[i] += q.v[i];
+        }
+    }
+    if (gl == 0) *tk = 0;
+    finish_row<T, VW, LPR, 1>(a, lr.x, lr.w, total, colbase, colok);
+}
+
+template <typename T, int VW, int LPR>
+static int launch_narrow(const SegArgs<T> &a, cudaStream_t stream) {
+    const int64_t units = ceil_div(a.n_direct, CGNN_SEG_NARROW_RPU) + a.n_items;
+    const int64_t gx = ceil_div(units, CGNN_SEG_THREADS / 32);
+    const int64_t gy = ceil_div(a.width, (int64_t)LPR * VW);
+    CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
+    seg_narrow_kernel<T, VW, LPR><<<dim3((unsigned)gx, (unsigned)gy), CGNN_SEG_THREADS, 0, stream>>>(a);
+    CGNN_LAUNCH_CHECK();
+    return CGNN_OK;
+}
+
 template <typename T, int VW, int LPR, int VPL, bool MASKED, bool GENERIC>
 static int launch_cfg(const SegArgs<T> &a, cudaStream_t stream) {
     constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR - 1;
@@ -357,6 +530,18 @@ static int launch_cfg(const SegArgs<T> &a, cudaStream_t stream) {
 template <typename T, int VW, bool MASKED, bool GENERIC>
 static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
     const int64_t vecs = a.width / VW;
+    if constexpr (!MASKED && !GENERIC) {
+#if CGNN_SEG_NARROW
+        // measured on B200: side-by-side groups win for 4-lane rows (F <= 16 fp32: 123 -> 68 us on
+        // the 325 k-node graph) and lose or tie from 8 lanes up, where each group keeps its own unit.
+        // Rows masked per group stay on seg_kernel so that both mask modes add in the same order.
+        if (vecs <= 4 && a.seg_mask == nullptr) return launch_narrow<T, VW, 4>(a, stream);
+#if CGNN_SEG_NARROW > 1
+        if (vecs <= 8) return launch_narrow<T, VW, 8>(a, stream);
+        if (vecs <= 16) return launch_narrow<T, VW, 16>(a, stream);
+#endif
+#endif
+    }
     if (vecs <= 4) return launch_cfg<T, VW, 4, 1, MASKED, GENERIC>(a, stream);
     if (vecs <= 8) return launch_cfg<T, VW, 8, 1, MASKED, GENERIC>(a, stream);
     if (vecs <= 16) return launch_cfg<T, VW, 16, 1, MASKED, GENERIC>(a, stream);
