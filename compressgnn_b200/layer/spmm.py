@@ -33,29 +33,39 @@ def _timed(record, name, launch):
     return result
 
 
-def _forward(graph, x, record=None):
+def _rule_buffer(graph, like, given):
+    """The rule matrix of one pass: a caller-kept buffer (already placed with
+    ``empty_row_aligned`` against ``like``) or a fresh one."""
+    if given is None:
+        return _native.empty_row_aligned(graph.rule_cnt, like)
+    if given.shape != (graph.rule_cnt, like.size(1)) or given.dtype != like.dtype:
+        raise RuntimeError("rule buffer does not match the graph and the feature matrix")
+    return given
+
+
+def _forward(graph, x, record=None, out=None, rule_out=None):
     _require_cuda(x)
     x = x.contiguous()
     plan = graph.propagation_plan()
     dt = x.dtype
     # rule_out is placed a whole number of rows away from x so that the fused pass over
     # (rule_out, x) addresses both matrices with one base pointer
-    rule_out = _native.empty_row_aligned(graph.rule_cnt, x)
+    rule_out = _rule_buffer(graph, x, rule_out)
     _timed(record, "fwd_r2v", lambda: _native.spmm_with_plan(
         plan.r2v, graph.r2v_graph.value_as(dt), x, out=rule_out))
     for i, (level_plan, level) in enumerate(zip(plan.levels, graph.r2r_graph)):
         _timed(record, f"fwd_level{i}", lambda: _native.spmm_with_plan(
             level_plan, level.value_as(dt), rule_out, out=rule_out, accumulate=True))
     return _timed(record, "fwd_out", lambda: _native.spmm_pair_with_plan(
-        plan.out, graph.v2r_graph.value_as(dt), rule_out, graph.v2v_graph.value_as(dt), x))
+        plan.out, graph.v2r_graph.value_as(dt), rule_out, graph.v2v_graph.value_as(dt), x, out=out))
 
 
-def _backward(graph, grad, record=None):
+def _backward(graph, grad, record=None, out=None, rule_out=None):
     _require_cuda(grad)
     grad = grad.contiguous()
     plan = graph.propagation_plan()
     dt = grad.dtype
-    rule_out = _native.empty_row_aligned(graph.rule_cnt, grad)
+    rule_out = _rule_buffer(graph, grad, rule_out)
     _timed(record, "bwd_v2r_t", lambda: _native.spmm_with_plan(
         plan.v2r_t, graph.v2r_graph.value_as(dt, True), grad, out=rule_out))
     levels = list(enumerate(zip(plan.levels_t, graph.r2r_graph)))
@@ -63,7 +73,8 @@ def _backward(graph, grad, record=None):
         _timed(record, f"bwd_level{i}", lambda: _native.spmm_with_plan(
             level_plan, level.value_as(dt, True), rule_out, out=rule_out, accumulate=True))
     return _timed(record, "bwd_out", lambda: _native.spmm_pair_with_plan(
-        plan.out_t, graph.v2v_graph.value_as(dt, True), grad, graph.r2v_graph.value_as(dt, True), rule_out))
+        plan.out_t, graph.v2v_graph.value_as(dt, True), grad, graph.r2v_graph.value_as(dt, True), rule_out,
+        out=out))
 
 
 def compress_spmm(graph, x_j):

@@ -259,3 +259,37 @@ def test_gcn_with_both_compressions_trains_one_step():
     model.set_epoch(1)
     assert torch.isfinite(model(data.x, data.edge_index)).all()
     assert model.layers[0].cluster.refresh_count == 1  # reused at epoch 1
+
+
+@pytest.mark.parametrize("depth", [1, 2, 3])
+def test_host_propagation_queue_matches_resident_passes(depth):
+    """Passes queued on host matrices (upload / propagate / download streams over a ring of
+    device buffers) deliver the bits of the resident passes, whatever the ring depth, and the
+    resident result matches the oracle."""
+    from compressgnn_b200.layer import HostPropagation
+    from compressgnn_b200.layer import spmm as spmm_layer
+    data = make_data(n=3000, width=40)
+    blocks = oracle_blocks(data.edge_index)
+    data.to("cuda")
+    graph = data.edge_index
+    n = data.vertex_cnt
+    pipe = HostPropagation(graph, 40, depth=depth)
+    gen = torch.Generator().manual_seed(depth)
+    sources = [torch.randn(n, 40, generator=gen).pin_memory() for _ in range(7)]
+    results = [torch.full((n, 40), float("nan")).pin_memory() for _ in range(7)]
+    events = []
+    for i, (src, dst) in enumerate(zip(sources, results)):
+        events.append(pipe.forward(src, dst) if i % 2 == 0 else pipe.backward(src, dst))
+    events[2].synchronize()
+    assert torch.equal(results[0], spmm_layer._forward(graph, sources[0].cuda()).cpu())
+    pipe.synchronize()
+    for i, (src, dst) in enumerate(zip(sources, results)):
+        one_pass = spmm_layer._forward if i % 2 == 0 else spmm_layer._backward
+        assert torch.equal(dst, one_pass(graph, src.cuda()).cpu()), f"pass {i}"
+    assert_close_rel(results[0].numpy(), oracle.propagate_forward(blocks, sources[0].numpy()), what="forward")
+    assert_close_rel(results[1].numpy(), oracle.propagate_backward(blocks, sources[1].numpy(), n, data.rule_cnt),
+                     what="backward")
+    with pytest.raises(RuntimeError):
+        pipe.forward(sources[0][:, :8].contiguous(), results[0])
+    with pytest.raises(RuntimeError):
+        pipe.forward(sources[0].cuda(), results[0])
