@@ -503,6 +503,291 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS) seg_narrow_kernel(const SegA
     finish_row<T, VW, LPR, 1>(a, lr.x, lr.w, total, colbase, colok);
 }
 
+// ---------------------------------------------------------------------------------------
+// Wide rows (more than 16 vectors, i.e. at least 272 bytes of a row per column tile): the gathered
+// rows are staged through shared memory by bulk asynchronous copies (cp.async.bulk, completion
+// counted on an mbarrier) instead of being loaded into registers.  A warp owns a ring of
+// S stages x B rows; the lane that holds an entry of the unit's stream issues the copy of its
+// source row (so the address of an entry, including the choice between the two source matrices,
+// is computed once by one lane); when a stage's barrier completes the warp moves the stage to
+// registers, refills it at once and then adds the rows to its row sums.  Copies stay in flight
+// while rows are finished and written, and what is in flight per SM is bounded by shared memory,
+// not registers.  Measured on B200: CTAs of ONE warp with an 8 KB ring (about 24 per SM) beat
+// larger CTAs with deeper rings by 20 % -- units differ in length, and a CTA's shared memory is
+// idle from the moment its first warp finishes until its last one does.  Unit decomposition, row
+// order, chunk tickets and summation order are those of seg_kernel, so both kernels produce the
+// same bits.
+// ---------------------------------------------------------------------------------------
+#ifndef CGNN_SEG_BULK
+#define CGNN_SEG_BULK 1
+#endif
+#ifndef CGNN_SEG_BULK_WARPS
+#define CGNN_SEG_BULK_WARPS 1        // warps per CTA: one, so that a finished unit frees its ring at once
+#endif
+#ifndef CGNN_SEG_BULK_STAGE_BYTES
+#define CGNN_SEG_BULK_STAGE_BYTES 4096  // one stage: 4 rows of a 1 KB tile, 8 rows of a 512-byte tile
+#endif
+#ifndef CGNN_SEG_BULK_S
+#define CGNN_SEG_BULK_S 2
+#endif
+#ifndef CGNN_SEG_BULK_RPU
+#define CGNN_SEG_BULK_RPU CGNN_SEG_RPU  // rows per direct work unit of the staged kernel
+#endif
+constexpr int BULK_WAIT_LIMIT = 1 << 20;  // mbarrier polls before a stage is given up
+
+__device__ __forceinline__ uint32_t shared_addr(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(shared_addr(bar)), "r"(arrivals));
+}
+__device__ __forceinline__ void mbar_arrive_expect(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_addr(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(done)
+        : "r"(shared_addr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+// Poll with a limit; true when the phase completed.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+    for (int i = 0; i < BULK_WAIT_LIMIT; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// Global -> shared bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned) that
+// reports to `bar`.  The destination is this CTA's own shared memory.
+__device__ __forceinline__ void bulk_copy_to_shared(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     shared_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(shared_addr(bar))
+                 : "memory");
+}
+
+template <typename T, int VPL>
+struct BulkLayout {
+    static constexpr int SLOT = 32 * VPL * 16;  // bytes of one staged row tile
+    static constexpr int W = CGNN_SEG_BULK_WARPS, B = CGNN_SEG_BULK_STAGE_BYTES / SLOT, S = CGNN_SEG_BULK_S;
+    static constexpr size_t RING = (size_t)S * B * SLOT;
+    static constexpr size_t BARS = (size_t)W * RING;
+    static constexpr size_t META = BARS + (size_t)W * S * 8;
+    static constexpr size_t BYTES = META + (size_t)W * S * B * sizeof(T);
+};
+
+template <typename T, int VW, int VPL>
+__global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(const SegArgs<T> a) {
+    using V = Vec<T, VW>;
+    using L = BulkLayout<T, VPL>;
+    static_assert(sizeof(T) * VW == 16, "bulk staging moves 16-byte vectors");
+    static_assert(32 % L::B == 0, "a stage must not straddle two entry windows");
+    constexpr int LPR = 32, B = L::B, S = L::S, SLOT = L::SLOT;
+    constexpr int TILE = 32 * VPL * VW;  // columns of one tile
+    constexpr int RPU = CGNN_SEG_BULK_RPU;
+    constexpr unsigned FULL = 0xffffffffu;
+    extern __shared__ __align__(128) unsigned char bulk_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned char *ring = bulk_smem + (size_t)warp * L::RING;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(bulk_smem + L::BARS) + warp * S;
+    T *meta = reinterpret_cast<T *>(bulk_smem + L::META) + warp * (S * B);
+
+    const int64_t unit = (int64_t)blockIdx.x * L::W + warp;
+    const int64_t width = a.width;
+    const int64_t col0 = (int64_t)blockIdx.y * TILE;
+    const int64_t colbase = col0 + lane * VW;
+    const uint32_t slot_bytes = (uint32_t)(min((int64_t)TILE, width - col0) * (int64_t)sizeof(T));
+    bool colok[VPL];
+    V acc[VPL];
+#pragma unroll
+    for (int p = 0; p < VPL; ++p) {
+        colok[p] = colbase + p * (LPR * VW) < width;
+        acc[p] = vec_zero<T, VW>();
+    }
+    const int64_t direct_units = (a.n_direct + RPU - 1) / RPU;
+
+    int e_begin, e_end, nr = 0, myptr = 0;
+    int32_t myrow = 0;
+    int64_t item_index = -1;
+    if (unit < direct_units) {
+        const int64_t first = unit * RPU;
+        nr = (int)min((int64_t)RPU, a.n_direct - first);
+        if (lane <= nr) myptr = a.uptr[first + lane];
+        if (lane < nr) myrow = a.urow ? a.urow[first + lane] : (int32_t)(first + lane);
+        e_begin = __shfl_sync(FULL, myptr, 0);
+        e_end = __shfl_sync(FULL, myptr, nr);
+    } else {
+        item_index = unit - direct_units;
+        if (item_index >= a.n_items) return;  // whole warp
+        const int4 item = a.items[item_index];
+        e_begin = item.y;
+        e_end = item.z;
+    }
+    if (lane < S) mbar_init(&bars[lane], 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    __syncwarp();
+
+    int cur = 0;
+    int row_begin = e_begin;
+    int row_end = item_index >= 0 ? e_end : __shfl_sync(FULL, myptr, 1);
+    auto flush = [&]() {  // finish listed row `cur` and move to the next one
+        const int32_t row = __shfl_sync(FULL, myrow, cur);
+        finish_row<T, VW, LPR, VPL>(a, row, row_begin < row_end ? row_begin : -1, acc, colbase, colok);
+#pragma unroll
+        for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
+        ++cur;
+        row_begin = row_end;
+        row_end = __shfl_sync(FULL, myptr, (cur + 1) & 31);
+    };
+
+    // ---- issue side: a window of 32 entries in registers (lane l holds entry window*32 + l) ----
+    const int n_ent = e_end - e_begin;
+    const int nb = (n_ent + B - 1) / B;
+    const T *src1 = a.src0 + a.delta_elems;
+    int32_t o = 0, o_next = 0;
+    T v = T(1), v_next = T(1);
+    if (lane < n_ent) {
+        o = a.entries[e_begin + lane];
+        if (a.val) v = a.val[e_begin + lane];
+    }
+    if (32 + lane < n_ent) {
+        o_next = a.entries[e_begin + 32 + lane];
+        if (a.val) v_next = a.val[e_begin + 32 + lane];
+    }
+    int window = 0;
+    auto issue = [&](int b) {
+        const int first = b * B;  // position of the stage's first entry in the unit's stream
+        if ((first >> 5) != window) {
+            window = first >> 5;
+            o = o_next;
+            v = v_next;
+            const int nxt = (window + 1) * 32 + lane;
+            if (nxt < n_ent) {
+                o_next = a.entries[e_begin + nxt];
+                if (a.val) v_next = a.val[e_begin + nxt];
+            }
+        }
+        const int st = b % S;
+        const int j = lane - (first & 31);
+        const int cnt = min(B, n_ent - first);
+        if (j == 0) mbar_arrive_expect(&bars[st], (uint32_t)cnt * slot_bytes);
+        __syncwarp();
+        if (j >= 0 && j < cnt) {
+            const T *row = (o < 0 ? src1 : a.src0) + (int64_t)(o & 0x7fffffff) * width + col0;
+            meta[st * B + j] = v;
+            bulk_copy_to_shared(ring + (size_t)(st * B + j) * SLOT, row, slot_bytes, &bars[st]);
+        }
+    };
+    for (int b = 0; b < S && b < nb; ++b) issue(b);
+
+    // ---- consume side ---------------------------------------------------------------------------
+    int b = 0;
+    bool expired = false;
+    for (; b < nb; ++b) {
+        const int st = b % S;
+        if (!__all_sync(FULL, mbar_wait_bounded(&bars[st], (uint32_t)(b / S) & 1u))) {
+            expired = true;
+            break;
+        }
+        __syncwarp();  // the issuing lanes' value words are visible to the whole warp
+        const int ebase = e_begin + b * B;
+        const int cnt = min(B, e_end - ebase);
+        const unsigned char *stage = ring + (size_t)st * B * SLOT + lane * 16;
+        // the stage moves to registers and is handed back for refilling before the arithmetic
+        V x[B][VPL];
+        T w[B];
+#pragma unroll
+        for (int j = 0; j < B; ++j) {
+            w[j] = meta[st * B + j];
+#pragma unroll
+            for (int p = 0; p < VPL; ++p) x[j][p] = *reinterpret_cast<const V *>(stage + j * SLOT + p * 512);
+        }
+        __syncwarp();  // every lane has read the stage
+        if (b + S < nb) issue(b + S);
+        if (ebase + cnt <= row_end) {  // no row ends inside this stage
+#pragma unroll
+            for (int j = 0; j < B; ++j)
+                if (j < cnt) fma_row<T, VW, VPL>(acc, x[j], w[j], colok);
+        } else {
+#pragma unroll
+            for (int j = 0; j < B; ++j) {
+                if (j < cnt) {
+                    while (ebase + j >= row_end) flush();
+                    fma_row<T, VW, VPL>(acc, x[j], w[j], colok);
+                }
+            }
+        }
+    }
+    if (expired) {
+        // give up on this unit: record it, let the copies still in flight land (bounded), write nothing
+        if (lane == 0) atomicOr(&g_seg_status, STATUS_WAIT_EXPIRED);
+        for (int bb = b + 1; bb < nb && bb < b + S; ++bb) mbar_wait_bounded(&bars[bb % S], (uint32_t)(bb / S) & 1u);
+        return;
+    }
+    if (item_index < 0) {
+        while (cur < nr) flush();
+        return;
+    }
+
+    // ---- chunk of a long row: publish the partial sum, the last ticket adds them up --------
+    const int4 item = a.items[item_index];
+    const int4 lr = a.longs[item.x];
+    T *part = a.partial + item_index * width + colbase;
+#pragma unroll
+    for (int p = 0; p < VPL; ++p)
+        if (colok[p]) vec_store<T, VW>(part + p * (LPR * VW), acc[p]);
+    __threadfence();
+    __syncwarp();
+    int *tk = a.tickets + (int64_t)item.x * gridDim.y + blockIdx.y;
+    int ticket = 0;
+    if (lane == 0) ticket = atomicAdd(tk, 1);
+    ticket = __shfl_sync(FULL, ticket, 0);
+    if (ticket != lr.z - 1) return;
+    __threadfence();
+#pragma unroll
+    for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
+    for (int s = 0; s < lr.z; ++s) {
+        const T *ps = a.partial + (int64_t)(lr.y + s) * width + colbase;
+#pragma unroll
+        for (int p = 0; p < VPL; ++p) {
+            if (colok[p]) {
+                const V q = vec_load_cg<T, VW>(ps + p * (LPR * VW));
+#pragma unroll
+                for (int i = 0; i < VW; ++i) acc[p].v[i] += q.v[i];
+            }
+        }
+    }
+    if (lane == 0) *tk = 0;  // leave the ticket ready for the next launch
+    finish_row<T, VW, LPR, VPL>(a, lr.x, lr.w, acc, colbase, colok);
+}
+
+template <typename T, int VW, int VPL>
+static int launch_bulk(const SegArgs<T> &a, cudaStream_t stream) {
+    using L = BulkLayout<T, VPL>;
+    static std::mutex mu;
+    static uint64_t configured = 0;  // one bit per device: the kernel may use L::BYTES of shared memory
+    int device = 0;
+    CGNN_CUDA(cudaGetDevice(&device));
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (device >= 64 || !(configured >> device & 1)) {
+            CGNN_CUDA(cudaFuncSetAttribute(seg_bulk_kernel<T, VW, VPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)L::BYTES));
+            if (device < 64) configured |= 1ull << device;
+        }
+    }
+    const int64_t units = ceil_div(a.n_direct, CGNN_SEG_BULK_RPU) + a.n_items;
+    const int64_t gx = ceil_div(units, L::W);
+    const int64_t gy = ceil_div(a.width, (int64_t)32 * VPL * VW);
+    CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
+    seg_bulk_kernel<T, VW, VPL><<<dim3((unsigned)gx, (unsigned)gy), L::W * 32, L::BYTES, stream>>>(a);
+    CGNN_LAUNCH_CHECK();
+    return CGNN_OK;
+}
+
 template <typename T, int VW, int LPR>
 static int launch_narrow(const SegArgs<T> &a, cudaStream_t stream) {
     const int64_t units = ceil_div(a.n_direct, CGNN_SEG_NARROW_RPU) + a.n_items;
@@ -542,6 +827,13 @@ static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
 #endif
 #endif
     }
+#if CGNN_SEG_BULK
+    if constexpr (!MASKED && sizeof(T) * VW == 16) {
+        // staged rows: measured faster than register gathers from 17 vectors (272 bytes) up
+        if (vecs > 32) return launch_bulk<T, VW, 2>(a, stream);
+        if (vecs > 16) return launch_bulk<T, VW, 1>(a, stream);
+    }
+#endif
     if (vecs <= 4) return launch_cfg<T, VW, 4, 1, MASKED, GENERIC>(a, stream);
     if (vecs <= 8) return launch_cfg<T, VW, 8, 1, MASKED, GENERIC>(a, stream);
     if (vecs <= 16) return launch_cfg<T, VW, 16, 1, MASKED, GENERIC>(a, stream);
@@ -553,9 +845,10 @@ static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
 
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// Tickets are kept per (long row, column tile).  The scalar path has the narrowest tiles
-// (256 columns), so this bounds gridDim.y of every configuration launch_vw can pick.
-static int64_t ticket_tiles(int64_t width) { return std::max<int64_t>(1, ceil_div(width, 256)); }
+// Tickets are kept per (long row, column tile).  The staged path in fp64 has the narrowest tiles
+// of a multi-tile launch (128 columns), so this bounds gridDim.y of every configuration
+// launch_vw can pick.
+static int64_t ticket_tiles(int64_t width) { return std::max<int64_t>(1, ceil_div(width, 128)); }
 
 template <typename T>
 static int run_typed(const cgnn_plan *p, int64_t width, const T *val, const T *src0, const T *src1,
