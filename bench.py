@@ -48,8 +48,8 @@ WORKLOADS = {
 }
 COMPRESS = dict(min_pair_frequency=4, threshold=4, max_depth=3, min_edge=1000000)
 # dram__bytes_read.sum + dram__bytes_write.sum of one forward fused vertex pass at N=1, from the
-# ncu capture summarised in profiles/seg_kernel_fused_vertex_pass_config2.md (same workload).
-NCU_TRAFFIC_BYTES = {("propagation", 1): 1.444e9}
+# ncu capture summarised in profiles/seg_bulk_kernel_fused_vertex_pass_config2.md (same workload).
+NCU_TRAFFIC_BYTES = {("propagation", 1): 1.461e9}
 
 
 def build_graph(name):
@@ -216,7 +216,9 @@ def run_gpu(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
 
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.width:
+        wl["width"] = args.width
     if args.scaling == "weak":
         # every rank holds a full-width column block: the job's feature matrix is N x (F * world)
         width = wl["width"]
@@ -351,7 +353,7 @@ def run_gpu(args):
                  "ms_per_step_waiting_each_step": e2e_sync_sec * 1e3,
                  "api": "HostPropagation.forward/backward on pinned host matrices"} if e2e_sec else None),
         "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "seg_kernel (fused v2r+v2v vertex pass, forward)",
+        "roofline": {"bound": "hbm", "kernel": "seg_bulk_kernel (fused v2r+v2v vertex pass, forward)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_src, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, world)),
                      "algorithmic_bytes_per_launch": bytes_by_name[dom], "ms_per_launch": launch_ms[dom],
@@ -573,7 +575,9 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.width:
+        wl["width"] = args.width
     world = int(os.environ.get("WORLD_SIZE", "1"))
     data, e_orig = build_graph(args.workload)
     # The CPU has no GPUs to scale over: it runs one 256-column block per step whatever N is; in the
@@ -608,6 +612,8 @@ def main():
     ap.add_argument("--impl", choices=["cgnn", "reference"], default="cgnn")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cluster", "gcn"], default="propagation")
     ap.add_argument("--cluster-nodes", type=int, default=2450000)
+    ap.add_argument("--width", type=int, default=0,
+                    help="feature columns per GPU of a propagation workload (default: the workload's own)")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="weak: every GPU holds a full-width (256-column) block of a feature matrix that is "
                          "N x 256*gpus; strong: the 256 columns are divided among the GPUs")

@@ -155,8 +155,19 @@ __device__ __forceinline__ void fma_row(Vec<T, VW> (&acc)[VPL], const Vec<T, VW>
 #pragma unroll
     for (int p = 0; p < VPL; ++p) {
         if (colok[p]) {
+            if constexpr (sizeof(T) == 4 && VW == 4) {
+                // two packed fma.rn.f32x2 (sm_100): each half is the IEEE fma of the scalar form
+                const float2 ww = make_float2(w, w);
+                const float2 lo = __ffma2_rn(make_float2(x[p].v[0], x[p].v[1]), ww, make_float2(acc[p].v[0], acc[p].v[1]));
+                const float2 hi = __ffma2_rn(make_float2(x[p].v[2], x[p].v[3]), ww, make_float2(acc[p].v[2], acc[p].v[3]));
+                acc[p].v[0] = lo.x;
+                acc[p].v[1] = lo.y;
+                acc[p].v[2] = hi.x;
+                acc[p].v[3] = hi.y;
+            } else {
 #pragma unroll
-            for (int i = 0; i < VW; ++i) acc[p].v[i] = fma(x[p].v[i], w, acc[p].v[i]);
+                for (int i = 0; i < VW; ++i) acc[p].v[i] = fma(x[p].v[i], w, acc[p].v[i]);
+            }
         }
     }
 }
@@ -530,6 +541,9 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS) seg_narrow_kernel(const SegA
 #ifndef CGNN_SEG_BULK_S
 #define CGNN_SEG_BULK_S 2
 #endif
+#ifndef CGNN_SEG_BULK_MIN_VECS
+#define CGNN_SEG_BULK_MIN_VECS 17    // narrowest row (in 16-byte vectors) that is staged
+#endif
 #ifndef CGNN_SEG_BULK_RPU
 #define CGNN_SEG_BULK_RPU CGNN_SEG_RPU  // rows per direct work unit of the staged kernel
 #endif
@@ -575,7 +589,7 @@ struct BulkLayout {
     static constexpr int W = CGNN_SEG_BULK_WARPS, B = CGNN_SEG_BULK_STAGE_BYTES / SLOT, S = CGNN_SEG_BULK_S;
     static constexpr size_t RING = (size_t)S * B * SLOT;
     static constexpr size_t BARS = (size_t)W * RING;
-    static constexpr size_t META = BARS + (size_t)W * S * 8;
+    static constexpr size_t META = (BARS + (size_t)W * S * 8 + 15) / 16 * 16;
     static constexpr size_t BYTES = META + (size_t)W * S * B * sizeof(T);
 };
 
@@ -699,9 +713,15 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
         // the stage moves to registers and is handed back for refilling before the arithmetic
         V x[B][VPL];
         T w[B];
+        static_assert(B % VW == 0, "a stage's value words are read as whole vectors");
+#pragma unroll
+        for (int j = 0; j < B; j += VW) {
+            const V wv = *reinterpret_cast<const V *>(meta + st * B + j);
+#pragma unroll
+            for (int i = 0; i < VW; ++i) w[j + i] = wv.v[i];
+        }
 #pragma unroll
         for (int j = 0; j < B; ++j) {
-            w[j] = meta[st * B + j];
 #pragma unroll
             for (int p = 0; p < VPL; ++p) x[j][p] = *reinterpret_cast<const V *>(stage + j * SLOT + p * 512);
         }
@@ -831,7 +851,7 @@ static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
     if constexpr (!MASKED && sizeof(T) * VW == 16) {
         // staged rows: measured faster than register gathers from 17 vectors (272 bytes) up
         if (vecs > 32) return launch_bulk<T, VW, 2>(a, stream);
-        if (vecs > 16) return launch_bulk<T, VW, 1>(a, stream);
+        if (vecs >= CGNN_SEG_BULK_MIN_VECS) return launch_bulk<T, VW, 1>(a, stream);
     }
 #endif
     if (vecs <= 4) return launch_cfg<T, VW, 4, 1, MASKED, GENERIC>(a, stream);
@@ -849,6 +869,12 @@ static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t
 // of a multi-tile launch (128 columns), so this bounds gridDim.y of every configuration
 // launch_vw can pick.
 static int64_t ticket_tiles(int64_t width) { return std::max<int64_t>(1, ceil_div(width, 128)); }
+
+// Bytes at the start of a scratch buffer that must be zero before the first launch (and are
+// left zero by every launch): the tickets.
+static size_t zero_prefix_bytes(const cgnn_plan *p, int64_t width) {
+    return align_up((size_t)p->n_long * (size_t)ticket_tiles(width) * sizeof(int), 256);
+}
 
 template <typename T>
 static int run_typed(const cgnn_plan *p, int64_t width, const T *val, const T *src0, const T *src1,
@@ -879,8 +905,8 @@ static int run_typed(const cgnn_plan *p, int64_t width, const T *val, const T *s
 
     const bool vec = width % VWMAX == 0 && aligned16(src0) && aligned16(src1) &&
                      aligned16(mask) && aligned16(seg_mask) && aligned16(out);
-    const size_t ticket_bytes =
-        align_up((size_t)p->n_long * (size_t)ticket_tiles(width) * sizeof(int), 256);
+    // scratch: [tickets][one partial row per chunk]
+    const size_t ticket_bytes = zero_prefix_bytes(p, width);
     const size_t need = ticket_bytes + (size_t)p->n_items * (size_t)width * sizeof(T);
     if (p->n_items > 0) {
         CGNN_REQUIRE(scratch != nullptr && scratch_bytes >= need,
@@ -1308,7 +1334,7 @@ int cgnn_plan_permute_values(const cgnn_plan *p, int dtype, const void *val0, co
 size_t cgnn_plan_ticket_bytes(const cgnn_plan *p, int64_t width, int dtype) {
     if (!p || width <= 0) return 0;
     (void)dtype;
-    return align_up((size_t)p->n_long * (size_t)ticket_tiles(width) * sizeof(int), 256);
+    return zero_prefix_bytes(p, width);
 }
 
 size_t cgnn_plan_scratch_bytes(const cgnn_plan *p, int64_t width, int dtype) {
