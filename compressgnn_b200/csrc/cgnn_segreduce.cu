@@ -527,7 +527,9 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS) seg_narrow_kernel(const SegA
 // larger CTAs with deeper rings by 20 % -- units differ in length, and a CTA's shared memory is
 // idle from the moment its first warp finishes until its last one does.  Unit decomposition, row
 // order, chunk tickets and summation order are those of seg_kernel, so both kernels produce the
-// same bits.
+// same bits.  MASKED: every entry also brings the tile of its mask row (same row index in
+// mask_src) into the second half of the stage, and values whose mask is <= 0 are dropped as the
+// stage moves to registers.
 // ---------------------------------------------------------------------------------------
 #ifndef CGNN_SEG_BULK
 #define CGNN_SEG_BULK 1
@@ -583,20 +585,22 @@ __device__ __forceinline__ void bulk_copy_to_shared(void *dst, const void *src, 
                  : "memory");
 }
 
-template <typename T, int VPL>
+template <typename T, int VPL, bool MASKED>
 struct BulkLayout {
     static constexpr int SLOT = 32 * VPL * 16;  // bytes of one staged row tile
     static constexpr int W = CGNN_SEG_BULK_WARPS, B = CGNN_SEG_BULK_STAGE_BYTES / SLOT, S = CGNN_SEG_BULK_S;
-    static constexpr size_t RING = (size_t)S * B * SLOT;
+    static constexpr int PARTS = MASKED ? 2 : 1;  // a stage holds B source tiles, then their B mask tiles
+    static constexpr size_t RING = (size_t)S * PARTS * B * SLOT;
     static constexpr size_t BARS = (size_t)W * RING;
     static constexpr size_t META = (BARS + (size_t)W * S * 8 + 15) / 16 * 16;
     static constexpr size_t BYTES = META + (size_t)W * S * B * sizeof(T);
 };
 
-template <typename T, int VW, int VPL>
+template <typename T, int VW, int VPL, bool MASKED>
 __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(const SegArgs<T> a) {
     using V = Vec<T, VW>;
-    using L = BulkLayout<T, VPL>;
+    using L = BulkLayout<T, VPL, MASKED>;
+    constexpr int PARTS = L::PARTS;
     static_assert(sizeof(T) * VW == 16, "bulk staging moves 16-byte vectors");
     static_assert(32 % L::B == 0, "a stage must not straddle two entry windows");
     constexpr int LPR = 32, B = L::B, S = L::S, SLOT = L::SLOT;
@@ -687,12 +691,16 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
         const int st = b % S;
         const int j = lane - (first & 31);
         const int cnt = min(B, n_ent - first);
-        if (j == 0) mbar_arrive_expect(&bars[st], (uint32_t)cnt * slot_bytes);
+        if (j == 0) mbar_arrive_expect(&bars[st], (uint32_t)(cnt * PARTS) * slot_bytes);
         __syncwarp();
         if (j >= 0 && j < cnt) {
-            const T *row = (o < 0 ? src1 : a.src0) + (int64_t)(o & 0x7fffffff) * width + col0;
+            const int64_t off = (int64_t)(o & 0x7fffffff) * width + col0;
             meta[st * B + j] = v;
-            bulk_copy_to_shared(ring + (size_t)(st * B + j) * SLOT, row, slot_bytes, &bars[st]);
+            bulk_copy_to_shared(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off, slot_bytes,
+                                &bars[st]);
+            if constexpr (MASKED)
+                bulk_copy_to_shared(ring + (size_t)(st * PARTS * B + B + j) * SLOT, a.mask_src + off, slot_bytes,
+                                    &bars[st]);
         }
     };
     for (int b = 0; b < S && b < nb; ++b) issue(b);
@@ -709,7 +717,7 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
         __syncwarp();  // the issuing lanes' value words are visible to the whole warp
         const int ebase = e_begin + b * B;
         const int cnt = min(B, e_end - ebase);
-        const unsigned char *stage = ring + (size_t)st * B * SLOT + lane * 16;
+        const unsigned char *stage = ring + (size_t)st * PARTS * B * SLOT + lane * 16;
         // the stage moves to registers and is handed back for refilling before the arithmetic
         V x[B][VPL];
         T w[B];
@@ -723,7 +731,15 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
 #pragma unroll
         for (int j = 0; j < B; ++j) {
 #pragma unroll
-            for (int p = 0; p < VPL; ++p) x[j][p] = *reinterpret_cast<const V *>(stage + j * SLOT + p * 512);
+            for (int p = 0; p < VPL; ++p) {
+                x[j][p] = *reinterpret_cast<const V *>(stage + j * SLOT + p * 512);
+                if constexpr (MASKED) {  // entries whose mask value is <= 0 contribute 0
+                    const V m = *reinterpret_cast<const V *>(stage + (B + j) * SLOT + p * 512);
+#pragma unroll
+                    for (int i = 0; i < VW; ++i)
+                        if (m.v[i] <= T(0)) x[j][p].v[i] = T(0);
+                }
+            }
         }
         __syncwarp();  // every lane has read the stage
         if (b + S < nb) issue(b + S);
@@ -784,9 +800,9 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
     finish_row<T, VW, LPR, VPL>(a, lr.x, lr.w, acc, colbase, colok);
 }
 
-template <typename T, int VW, int VPL>
+template <typename T, int VW, int VPL, bool MASKED>
 static int launch_bulk(const SegArgs<T> &a, cudaStream_t stream) {
-    using L = BulkLayout<T, VPL>;
+    using L = BulkLayout<T, VPL, MASKED>;
     static std::mutex mu;
     static uint64_t configured = 0;  // one bit per device: the kernel may use L::BYTES of shared memory
     int device = 0;
@@ -794,7 +810,7 @@ static int launch_bulk(const SegArgs<T> &a, cudaStream_t stream) {
     {
         std::lock_guard<std::mutex> lock(mu);
         if (device >= 64 || !(configured >> device & 1)) {
-            CGNN_CUDA(cudaFuncSetAttribute(seg_bulk_kernel<T, VW, VPL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            CGNN_CUDA(cudaFuncSetAttribute(seg_bulk_kernel<T, VW, VPL, MASKED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)L::BYTES));
             if (device < 64) configured |= 1ull << device;
         }
@@ -803,7 +819,7 @@ static int launch_bulk(const SegArgs<T> &a, cudaStream_t stream) {
     const int64_t gx = ceil_div(units, L::W);
     const int64_t gy = ceil_div(a.width, (int64_t)32 * VPL * VW);
     CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
-    seg_bulk_kernel<T, VW, VPL><<<dim3((unsigned)gx, (unsigned)gy), L::W * 32, L::BYTES, stream>>>(a);
+    seg_bulk_kernel<T, VW, VPL, MASKED><<<dim3((unsigned)gx, (unsigned)gy), L::W * 32, L::BYTES, stream>>>(a);
     CGNN_LAUNCH_CHECK();
     return CGNN_OK;
 }
@@ -848,10 +864,10 @@ static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
 #endif
     }
 #if CGNN_SEG_BULK
-    if constexpr (!MASKED && sizeof(T) * VW == 16) {
+    if constexpr (sizeof(T) * VW == 16) {
         // staged rows: measured faster than register gathers from 17 vectors (272 bytes) up
-        if (vecs > 32) return launch_bulk<T, VW, 2>(a, stream);
-        if (vecs >= CGNN_SEG_BULK_MIN_VECS) return launch_bulk<T, VW, 1>(a, stream);
+        if (vecs > 32) return launch_bulk<T, VW, 2, MASKED>(a, stream);
+        if (vecs >= CGNN_SEG_BULK_MIN_VECS) return launch_bulk<T, VW, 1, MASKED>(a, stream);
     }
 #endif
     if (vecs <= 4) return launch_cfg<T, VW, 4, 1, MASKED, GENERIC>(a, stream);

@@ -149,7 +149,7 @@ def test_golden_mean_and_reconstruct(rt, golden):
 
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float64])
-@pytest.mark.parametrize("width", [1, 31, 33, 128, 602])
+@pytest.mark.parametrize("width", [1, 31, 33, 128, 256, 520, 602])
 @pytest.mark.parametrize("relu", [False, True])
 def test_reconstruct_grid(rt, dtype, width, relu):
     """Grid of reference tests/test_transformation.py:44-54, including unused groups."""
