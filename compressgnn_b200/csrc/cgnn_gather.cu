@@ -9,6 +9,12 @@
 
 #include "cgnn_plan.h"
 
+#ifndef CGNN_EXPAND_WIDE
+#define CGNN_EXPAND_WIDE 1
+#endif
+#ifndef CGNN_EXPAND_WIDE_MINBLOCKS
+#define CGNN_EXPAND_WIDE_MINBLOCKS 3
+#endif
 #ifndef CGNN_EXPAND_RPG
 #define CGNN_EXPAND_RPG 4
 #endif
@@ -93,6 +99,93 @@ __global__ void __launch_bounds__(256) expand_kernel(const ExpandArgs<T> a) {
     }
 }
 
+// Rows of more than 16 vectors without a divisor (the fused reconstruction and the mean backward
+// at benchmark widths): a warp expands 32 node rows per step, each lane owns VPL vectors of a row,
+// and bias / ReLU are compile-time switches, so that the per-row work is one index shuffle, one
+// row-base multiply, VPL loads, the epilogue and VPL streaming stores.
+template <typename T, int VW, int VPL, int U, bool BIAS, bool RELU>
+__global__ void __launch_bounds__(256, CGNN_EXPAND_WIDE_MINBLOCKS) expand_wide_kernel(const ExpandArgs<T> a) {
+    using V = Vec<T, VW>;
+    constexpr unsigned FULL = 0xffffffffu;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    const int64_t vecs = a.width / VW;
+    for (int64_t r0 = warp * 32; r0 < a.n; r0 += nwarps * 32) {
+        int32_t gi = -1;
+        if (r0 + lane < a.n) {
+            const int64_t g = a.index[r0 + lane];
+            if (g < 0 || g >= a.groups) atomicOr(&g_gather_status, STATUS_BAD_INDEX);
+            else gi = (int32_t)g;
+        }
+        const int cnt = (int)min((int64_t)32, a.n - r0);
+        for (int64_t cbase = 0; cbase < vecs; cbase += 32 * VPL) {  // uniform trip count
+            bool act[VPL];
+            int64_t col[VPL];
+            V b[VPL];
+#pragma unroll
+            for (int p = 0; p < VPL; ++p) {
+                const int64_t c = cbase + p * 32 + lane;
+                act[p] = c < vecs;
+                col[p] = c * VW;
+                b[p] = vec_zero<T, VW>();
+                if (BIAS && act[p]) b[p] = vec_load<T, VW>(a.bias + col[p]);
+            }
+            T *orow = a.out + r0 * a.width;
+            for (int j = 0; j < cnt; j += U) {
+                V x[U][VPL];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int32_t g = __shfl_sync(FULL, gi, (j + u) & 31);
+                    const bool live = j + u < cnt && g >= 0;  // a bad index yields zeros
+                    const T *trow = a.table + (int64_t)(live ? g : 0) * a.width;
+#pragma unroll
+                    for (int p = 0; p < VPL; ++p) {
+                        x[u][p] = vec_zero<T, VW>();
+                        if (live && act[p]) x[u][p] = vec_load<T, VW>(trow + col[p]);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    if (j + u < cnt) {
+#pragma unroll
+                        for (int p = 0; p < VPL; ++p) {
+                            if (act[p]) {
+                                V y;
+#pragma unroll
+                                for (int k = 0; k < VW; ++k) {
+                                    T v = x[u][p].v[k];
+                                    if (BIAS) v += b[p].v[k];
+                                    y.v[k] = (RELU && v < T(0)) ? T(0) : v;
+                                }
+                                vec_store_cs<T, VW>(orow + col[p], y);
+                            }
+                        }
+                    }
+                    orow += a.width;
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int VW, int VPL>
+static int launch_expand_wide(const ExpandArgs<T> &a, cudaStream_t stream) {
+    constexpr int U = 8 / VPL;  // 8 vectors in flight per lane
+    const int64_t blocks = std::min<int64_t>(ceil_div(a.n, 32 * 8), 148 * 32);
+    const bool bias = a.bias != nullptr, relu = a.relu != 0;
+    if (bias && relu)
+        expand_wide_kernel<T, VW, VPL, U, true, true><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else if (bias)
+        expand_wide_kernel<T, VW, VPL, U, true, false><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else if (relu)
+        expand_wide_kernel<T, VW, VPL, U, false, true><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    else
+        expand_wide_kernel<T, VW, VPL, U, false, false><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    CGNN_LAUNCH_CHECK();
+    return CGNN_OK;
+}
+
 // table[g,:] / max(count[g],1) for the (small) group table, one thread per element.
 template <typename T>
 __global__ void scale_rows_kernel(const T *table, const int32_t *count, T *out, int64_t groups,
@@ -124,6 +217,12 @@ static int expand_typed(const ExpandArgs<T> &a, cudaStream_t stream) {
                      aligned16(a.bias);
     if (vec) {
         const int64_t vecs = a.width / VWMAX;
+#if CGNN_EXPAND_WIDE
+        if (vecs > 16 && a.div_counts == nullptr) {
+            if (vecs > 32) return launch_expand_wide<T, VWMAX, 2>(a, stream);
+            return launch_expand_wide<T, VWMAX, 1>(a, stream);
+        }
+#endif
         if (vecs <= 4) return launch_expand<T, VWMAX, 4>(a, stream);
         if (vecs <= 8) return launch_expand<T, VWMAX, 8>(a, stream);
         if (vecs <= 16) return launch_expand<T, VWMAX, 16>(a, stream);

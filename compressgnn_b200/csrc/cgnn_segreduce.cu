@@ -366,9 +366,12 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kern
 #ifndef CGNN_SEG_NARROW_RPU
 #define CGNN_SEG_NARROW_RPU 16
 #endif
+#ifndef CGNN_SEG_NARROW_THREADS
+#define CGNN_SEG_NARROW_THREADS 32  // one warp per CTA: a finished unit frees its slot at once (68 -> 58 us at F=16)
+#endif
 
 template <typename T, int VW, int LPR>
-__global__ void __launch_bounds__(CGNN_SEG_THREADS) seg_narrow_kernel(const SegArgs<T> a) {
+__global__ void __launch_bounds__(CGNN_SEG_NARROW_THREADS) seg_narrow_kernel(const SegArgs<T> a) {
     using V = Vec<T, VW>;
     constexpr int G = 32 / LPR;
     constexpr int U = 8;  // steps (G entries each) in flight per lane
@@ -827,10 +830,10 @@ static int launch_bulk(const SegArgs<T> &a, cudaStream_t stream) {
 template <typename T, int VW, int LPR>
 static int launch_narrow(const SegArgs<T> &a, cudaStream_t stream) {
     const int64_t units = ceil_div(a.n_direct, CGNN_SEG_NARROW_RPU) + a.n_items;
-    const int64_t gx = ceil_div(units, CGNN_SEG_THREADS / 32);
+    const int64_t gx = ceil_div(units, CGNN_SEG_NARROW_THREADS / 32);
     const int64_t gy = ceil_div(a.width, (int64_t)LPR * VW);
     CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
-    seg_narrow_kernel<T, VW, LPR><<<dim3((unsigned)gx, (unsigned)gy), CGNN_SEG_THREADS, 0, stream>>>(a);
+    seg_narrow_kernel<T, VW, LPR><<<dim3((unsigned)gx, (unsigned)gy), CGNN_SEG_NARROW_THREADS, 0, stream>>>(a);
     CGNN_LAUNCH_CHECK();
     return CGNN_OK;
 }
@@ -839,7 +842,7 @@ template <typename T, int VW, int LPR, int VPL, bool MASKED, bool GENERIC>
 static int launch_cfg(const SegArgs<T> &a, cudaStream_t stream) {
     constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR - 1;
     const int64_t units = ceil_div(a.n_direct, RPU) + a.n_items;
-    const int64_t per_block = (CGNN_SEG_THREADS / 32) * (32 / LPR);
+    const int64_t per_block = (CGNN_SEG_NARROW_THREADS / 32) * (32 / LPR);
     const int64_t gx = ceil_div(units, per_block);
     const int64_t gy = ceil_div(a.width, (int64_t)LPR * VPL * VW);
     CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
@@ -853,14 +856,15 @@ static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
     const int64_t vecs = a.width / VW;
     if constexpr (!MASKED && !GENERIC) {
 #if CGNN_SEG_NARROW
-        // measured on B200: side-by-side groups win for 4-lane rows (F <= 16 fp32: 123 -> 68 us on
-        // the 325 k-node graph) and lose or tie from 8 lanes up, where each group keeps its own unit.
-        // Rows masked per group stay on seg_kernel so that both mask modes add in the same order.
-        if (vecs <= 4 && a.seg_mask == nullptr) return launch_narrow<T, VW, 4>(a, stream);
-#if CGNN_SEG_NARROW > 1
-        if (vecs <= 8) return launch_narrow<T, VW, 8>(a, stream);
-        if (vecs <= 16) return launch_narrow<T, VW, 16>(a, stream);
-#endif
+        // measured on B200 (325 k-node graph, fused vertex pass, single-warp CTAs): side-by-side
+        // groups against one unit per group take 68 -> 58 us at F=16, 128 -> 89 us at F=32 and
+        // 189 -> 138 us at F=64.  Rows masked per group stay on seg_kernel so that both mask modes
+        // add in the same order.
+        if (a.seg_mask == nullptr) {
+            if (vecs <= 4) return launch_narrow<T, VW, 4>(a, stream);
+            if (vecs <= 8) return launch_narrow<T, VW, 8>(a, stream);
+            if (vecs <= 16) return launch_narrow<T, VW, 16>(a, stream);
+        }
 #endif
     }
 #if CGNN_SEG_BULK
