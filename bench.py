@@ -530,6 +530,7 @@ def run_gcn(args):
     graph.to("cuda")
     gen = torch.Generator(device="cuda").manual_seed(5)
     y = torch.randint(0, 47, (n,), device="cuda", generator=gen)
+    y_col = y.unsqueeze(1)
     report = {}
     for width in (16, 64, 256, 1024):
         x = torch.randn(n, width, device="cuda", generator=gen)
@@ -541,7 +542,9 @@ def run_gcn(args):
         def epoch(e):
             model.set_epoch(e)
             opt.zero_grad(set_to_none=True)
-            loss = torch.nn.functional.nll_loss(model(x, graph), y)
+            # mean negative log-likelihood of the labels, written as a gather: the same number as
+            # F.nll_loss, whose CUDA kernels take 0.5 ms per epoch at this size
+            loss = -model(x, graph).gather(1, y_col).mean()
             loss.backward()
             opt.step()
             return loss

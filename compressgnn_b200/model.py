@@ -1,7 +1,8 @@
 """The caller of the hot path: ``GNNLayer`` (propagate, then either a Linear on all nodes or
 cluster -> Linear on representatives -> fused reconstruct) and a GCN stack of them
 (ref: ``model/compressgnn/gcn.py:12-71``; the reference hard-wires three layers, here the
-depth is a parameter so the two-layer benchmark configurations can be built)."""
+depth is a parameter so the two-layer benchmark configurations can be built, and the ReLU
+after a hidden layer is handed to the layer so that it runs inside the reconstruct kernel)."""
 import torch
 import torch.nn.functional as F
 from torch import Tensor
@@ -11,8 +12,11 @@ from .layer import Compressgnn_Cluster, Compressgnn_Reconstruct, KPropagate
 
 class GNNLayer(torch.nn.Module):
     def __init__(self, in_features, out_features, param_H=1, use_transformation=False, refresh_interval=1,
-                 process_group=None):
+                 process_group=None, activation=None):
         super().__init__()
+        if activation not in (None, "relu"):
+            raise ValueError("activation must be None or 'relu'")
+        self.activation = activation  # applied to the layer's output (fused into the reconstruction)
         self.lin = torch.nn.Linear(in_features=in_features, out_features=out_features, bias=True)
         self.P = KPropagate()
         self.use_transformation = use_transformation
@@ -31,8 +35,10 @@ class GNNLayer(torch.nn.Module):
         x = self.P(x=x, edge_index=edge_index, edge_weight=edge_weight, vertex_cnt=vertex_cnt, rule_cnt=rule_cnt)
         if self.use_transformation:
             reps, index = self.cluster(x)
-            return self.reconstruct(F.linear(reps, self.lin.weight, None), index, bias=self.lin.bias)
-        return self.lin(x)
+            return self.reconstruct(F.linear(reps, self.lin.weight, None), index, bias=self.lin.bias,
+                                    activation=self.activation)
+        x = self.lin(x)
+        return x.relu() if self.activation == "relu" else x
 
 
 class GCN(torch.nn.Module):
@@ -42,7 +48,8 @@ class GCN(torch.nn.Module):
         dims = [in_features] + [hidden_features] * (num_layers - 1) + [out_features]
         self.layers = torch.nn.ModuleList(
             GNNLayer(dims[i], dims[i + 1], param_H=param_H, use_transformation=use_transformation,
-                     refresh_interval=refresh_interval) for i in range(num_layers))
+                     refresh_interval=refresh_interval, activation="relu" if i + 1 < num_layers else None)
+            for i in range(num_layers))
         self.dropout = dropout
 
     def set_epoch(self, epoch, loss=None):
@@ -57,10 +64,8 @@ class GCN(torch.nn.Module):
         last = len(self.layers) - 1
         for i, layer in enumerate(self.layers):
             x = layer(x=x, edge_index=edge_index, edge_weight=edge_weight, vertex_cnt=vertex_cnt, rule_cnt=rule_cnt)
-            if i != last:
-                x = x.relu()
-                if dropout:
-                    x = F.dropout(x, p=self.dropout, training=self.training)
+            if i != last and dropout:  # the hidden layers' ReLU is part of the layer (fused reconstruct)
+                x = F.dropout(x, p=self.dropout, training=self.training)
         return F.log_softmax(x, dim=1)
 
     def forward(self, x: Tensor, edge_index, edge_weight=None, vertex_cnt: int = 0, rule_cnt: int = 0) -> Tensor:
