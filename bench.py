@@ -520,55 +520,86 @@ def run_gcn(args):
     (use_transformation=True, H=16, refresh_interval=5) on the config-2 graph, 47 uniform classes,
     input feature width swept over 16/64/256/1024.  A step = one training epoch (forward, NLL loss
     on all nodes, backward, Adam step), timed after warm-up epochs as the reference's
-    benchmark/end2end/compressgnn_gcn.py does."""
+    benchmark/end2end/compressgnn_gcn.py does.  With N GPUs the feature columns of every layer are
+    sharded (strong scaling: the same model and matrix on more GPUs) and the graph is replicated."""
     import torch
+    import torch.distributed as dist
     from compressgnn_b200.model import GCN
-    torch.cuda.set_device(0)
+    from compressgnn_b200 import dist as cdist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
     data, e_orig = build_graph("propagation")
     graph = data.edge_index
     n = graph.vertex_cnt
-    graph.to("cuda")
-    gen = torch.Generator(device="cuda").manual_seed(5)
-    y = torch.randint(0, 47, (n,), device="cuda", generator=gen)
+    graph.to(device)
+    gen = torch.Generator(device=device).manual_seed(5)  # the same labels and features on every rank
+    y = torch.randint(0, 47, (n,), device=device, generator=gen)
     y_col = y.unsqueeze(1)
     report = {}
     for width in (16, 64, 256, 1024):
-        x = torch.randn(n, width, device="cuda", generator=gen)
+        x = torch.randn(n, width, device=device, generator=gen)
         torch.manual_seed(5)
         model = GCN(width, 47, hidden_features=128, param_H=16, dropout=0.3, use_transformation=True,
-                    refresh_interval=5, num_layers=2).cuda()
+                    refresh_interval=5, num_layers=2).to(device)
         opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+        if world > 1:
+            x = cdist.shard_columns(x, rank, world)
+            net = cdist.ShardedGCN(model, dist.group.WORLD)  # shares the parameters of `model`
+        else:
+            net = model
 
         def epoch(e):
-            model.set_epoch(e)
+            net.set_epoch(e)
             opt.zero_grad(set_to_none=True)
             # mean negative log-likelihood of the labels, written as a gather: the same number as
             # F.nll_loss, whose CUDA kernels take 0.5 ms per epoch at this size
-            loss = -model(x, graph).gather(1, y_col).mean()
+            loss = -net(x, graph).gather(1, y_col).mean()
             loss.backward()
+            if world > 1:
+                net.sync_gradients()
             opt.step()
             return loss
 
         for e in range(max(args.warmup, 3)):
             epoch(e)
-        model.reset_cache()
+        net.reset_cache()
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for e in range(args.steps):
             loss = epoch(e)
         stop.record()
         torch.cuda.synchronize()
-        report[str(width)] = {"epoch_ms": start.elapsed_time(stop) / args.steps, "final_loss": float(loss)}
-        del model, opt, x
+        ms = start.elapsed_time(stop) / args.steps
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        report[str(width)] = {"epoch_ms": ms, "final_loss": float(loss.detach())}
+        del model, net, opt, x
     from compressgnn_b200 import runtime as rt
     assert rt.device_status() == 0
-    line = {"metric": "gcn_epoch_ms", "value": report["256"]["epoch_ms"], "unit": "ms", "n_gpus": 1,
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {"metric": "gcn_epoch_ms", "value": report["256"]["epoch_ms"], "unit": "ms", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": report["256"]["epoch_ms"],
-            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "gcn: 2-layer GCN, propagation + transformation compression, config-2 graph",
                        "nodes": n, "orig_edges": e_orig, "rules": graph.rule_cnt, "levels": graph.step, "classes": 47,
-                       "hidden": 128, "bits": 16, "refresh_interval": 5, "compressor": COMPRESS},
+                       "hidden": 128, "bits": 16, "refresh_interval": 5, "compressor": COMPRESS,
+                       "parallelism": f"feature columns of every layer sharded over {world} GPU(s), graph replicated; "
+                                      "collectives: projection all-reduce on refresh epochs, representative "
+                                      "all-gather and gradient all-reduces every epoch"},
             "epoch_ms_by_feature_width": report, "gpu_launches": None}
     print(json.dumps(line))
 

@@ -7,6 +7,11 @@ Only the LSH assignment needs whole rows: each rank projects its block onto its 
 hyperplanes and the partial projections are summed with ONE all-reduce (NCCL over NVLink on
 GPUs, gloo in the CPU tests) before sign packing, after which every rank derives the same
 bucket ids, counts and permutation.
+
+A whole layer (``ShardedGNNLayer``, ``ShardedGCN``) needs two more, small exchanges because its
+Linear contracts over all feature columns: the ``[B, F/G]`` blocks of the bucket representatives
+are gathered in front of it (their gradients summed on the way back), and the gradients of
+weight rows owned by different ranks are summed before the optimiser step.
 """
 import torch
 import torch.distributed as dist
@@ -45,3 +50,135 @@ def gather_columns(local, group=None):
     parts = [torch.empty_like(local) for _ in range(world)]
     dist.all_gather(parts, local, group=group)
     return torch.cat(parts, dim=-1)
+
+
+class _GatherColumns(torch.autograd.Function):
+    """``[B, F/G]`` column blocks of all ranks -> ``[B, F]`` on every rank.
+
+    Backward: with ``replicated_consumer`` every rank computes the same thing from the gathered
+    matrix, so the incoming gradient is already the full one and the local block is cut out of
+    it; otherwise each rank consumed the matrix for its own slice of the outputs and the
+    gradients are summed over the ranks first.
+    """
+
+    @staticmethod
+    def forward(ctx, local, group, replicated_consumer):
+        ctx.group, ctx.replicated = group, replicated_consumer
+        ctx.rank, ctx.world = dist.get_rank(group), dist.get_world_size(group)
+        ctx.width = local.size(-1)
+        return gather_columns(local.contiguous(), group)
+
+    @staticmethod
+    def backward(ctx, grad):
+        grad = grad.contiguous()
+        if not ctx.replicated:
+            grad = grad.clone()
+            dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=ctx.group)
+        begin = ctx.rank * ctx.width
+        return grad[..., begin:begin + ctx.width].contiguous(), None, None
+
+
+def gather_columns_autograd(local, group=None, replicated_consumer=False):
+    """Differentiable ``gather_columns`` (equal block widths on all ranks)."""
+    return _GatherColumns.apply(local, group, replicated_consumer)
+
+
+class ShardedGNNLayer(torch.nn.Module):
+    """A ``GNNLayer`` with transformation compression, run on one column block per rank.
+
+    Built from a full layer (same weights on every rank).  Propagation, the bucket means and
+    the reconstruction act on the local ``[N, F/G]`` block; the assignment sums the partial
+    projections (inside ``Compressgnn_Cluster``); the Linear contracts over all feature
+    columns, so the small ``[B, F/G]`` representative blocks are gathered first.  With
+    ``shard_output`` the rank then produces only its block of the output columns (its rows of
+    the weight); without it (class scores, whose width need not divide) every rank produces
+    all output columns.
+    """
+
+    def __init__(self, layer, group=None, shard_output=True):
+        super().__init__()
+        from .layer import Compressgnn_Cluster, Compressgnn_Reconstruct, KPropagate
+        if not layer.use_transformation:
+            raise ValueError("ShardedGNNLayer needs a layer built with use_transformation=True")
+        self.group, self.shard_output = group, shard_output
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        full = layer.cluster
+        if full.in_feature % self.world or (shard_output and layer.lin.out_features % self.world):
+            raise ValueError("feature widths must divide by the number of ranks")
+        self.lin = layer.lin
+        self.activation = layer.activation
+        self.P = KPropagate()
+        self.cluster = Compressgnn_Cluster(
+            in_feature=full.in_feature // self.world, param_H=full.param_H, training=True, cache=True,
+            index_cache=False, refresh_interval=full.refresh_interval, process_group=group,
+            device=full.random_vectors.device, dtype=full.random_vectors.dtype)
+        with torch.no_grad():
+            self.cluster.random_vectors.copy_(shard_planes(full.random_vectors, self.rank, self.world))
+        self.reconstruct = Compressgnn_Reconstruct()
+
+    def set_epoch(self, epoch, loss=None):
+        self.cluster.set_epoch(epoch, loss=loss)
+
+    def reset_cache(self):
+        self.cluster.reset_cache()
+
+    def forward(self, x_local, edge_index, edge_weight=None, vertex_cnt=0, rule_cnt=0):
+        p = self.P(x=x_local, edge_index=edge_index, edge_weight=edge_weight, vertex_cnt=vertex_cnt,
+                   rule_cnt=rule_cnt)
+        reps_local, index = self.cluster(p)
+        reps = gather_columns_autograd(reps_local, self.group, replicated_consumer=not self.shard_output)
+        weight, bias = self.lin.weight, self.lin.bias
+        if self.shard_output:
+            begin, end = column_range(self.lin.out_features, self.rank, self.world)
+            weight, bias = weight[begin:end], bias[begin:end]
+        return self.reconstruct(torch.nn.functional.linear(reps, weight, None), index, bias=bias,
+                                activation=self.activation)
+
+
+class ShardedGCN(torch.nn.Module):
+    """A ``GCN`` (all layers with transformation compression) on column-sharded features.
+
+    ``forward`` takes this rank's ``[N, F/G]`` block of the input features and returns the full
+    ``[N, classes]`` log-probabilities on every rank.  Hidden layers keep their outputs sharded;
+    the last layer's output is replicated.  After ``backward`` call ``sync_gradients()``: a
+    hidden layer's weight rows are owned by one rank each, so their gradients are summed over
+    the ranks; the last layer's gradients are already identical everywhere.
+    """
+
+    def __init__(self, model, group=None):
+        super().__init__()
+        last = len(model.layers) - 1
+        self.group = group
+        self.dropout = model.dropout
+        self.layers = torch.nn.ModuleList(
+            ShardedGNNLayer(layer, group, shard_output=i != last) for i, layer in enumerate(model.layers))
+
+    def set_epoch(self, epoch, loss=None):
+        for layer in self.layers:
+            layer.set_epoch(epoch, loss=loss)
+
+    def reset_cache(self):
+        for layer in self.layers:
+            layer.reset_cache()
+
+    def forward(self, x_local, edge_index, edge_weight=None, vertex_cnt=0, rule_cnt=0, dropout=True):
+        last = len(self.layers) - 1
+        x = x_local
+        for i, layer in enumerate(self.layers):
+            x = layer(x, edge_index, edge_weight, vertex_cnt, rule_cnt)
+            if i != last and dropout:
+                x = torch.nn.functional.dropout(x, p=self.dropout, training=self.training)
+        return torch.nn.functional.log_softmax(x, dim=1)
+
+    def sync_gradients(self):
+        """Sum the hidden layers' parameter gradients over the ranks (one flat all-reduce)."""
+        grads = [p.grad for layer in self.layers if layer.shard_output for p in layer.lin.parameters()
+                 if p.grad is not None]
+        if not grads or dist.get_world_size(self.group) == 1:
+            return
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+        offset = 0
+        for g in grads:
+            g.copy_(flat[offset:offset + g.numel()].view_as(g))
+            offset += g.numel()

@@ -1,6 +1,8 @@
 """Column-sharded hot path on 2 GPUs (NCCL): shard-local propagation equals the columns of the
 single-GPU result; the cluster module with a process group gives every rank the assignment the
-oracle's sharded projection order predicts.  Skipped on a box with fewer than 2 GPUs."""
+oracle's sharded projection order predicts; a column-sharded two-layer GCN step (forward,
+gradients after ``sync_gradients``) equals plain torch on the full features.  Skipped on a box
+with fewer than 2 GPUs."""
 import os
 import socket
 import sys
@@ -77,6 +79,40 @@ def _worker(rank, world, port):
         assert_close_rel(reps.cpu().numpy(), ref_reps, what="sharded mean")
         y = Compressgnn_Reconstruct()(reps, index, activation="relu")
         assert torch.equal(y, reps.index_select(0, index).relu())
+
+        # a whole column-sharded GCN step against plain torch on the full features, using the
+        # assignment the sharded layers chose
+        from compressgnn_b200.model import GCN
+        classes = 5
+        torch.manual_seed(3)  # same weights and hyperplanes on every rank
+        model = GCN(width, classes, hidden_features=32, param_H=10, dropout=0.0, use_transformation=True,
+                    refresh_interval=5, num_layers=2).cuda()
+        sharded = cdist.ShardedGCN(model, dist.group.WORLD)
+        sharded.set_epoch(0)
+        labels = torch.from_numpy(rng.integers(0, classes, n)).cuda()
+        out = sharded(cdist.shard_columns(data.x, rank, world), data.edge_index, dropout=False)
+        assert out.shape == (n, classes)
+
+        def scatter_mean(t, index, groups):
+            sums = torch.zeros(groups, t.size(1), device=t.device).index_add_(0, index, t)
+            return sums / torch.bincount(index, minlength=groups).clamp_min(1).to(t.dtype)[:, None]
+
+        def layer_ref(layer, feats):
+            p = KPropagate()(feats, data.edge_index, None, data.vertex_cnt, data.rule_cnt)
+            index = layer.cluster.vertex_index
+            reps_ = scatter_mean(p, index, layer.cluster.active_bucket + 1)
+            return (reps_ @ layer.lin.weight.t()).index_select(0, index) + layer.lin.bias
+
+        ref = torch.log_softmax(layer_ref(sharded.layers[1], layer_ref(sharded.layers[0], data.x).relu()), 1)
+        torch.testing.assert_close(out, ref, atol=2e-4, rtol=1e-3)
+        torch.nn.functional.nll_loss(out, labels).backward()
+        sharded.sync_gradients()
+        params = list(model.parameters())
+        for p_, gr in zip(params, torch.autograd.grad(torch.nn.functional.nll_loss(ref, labels), params)):
+            torch.testing.assert_close(p_.grad, gr, atol=2e-4, rtol=1e-3)
+        outs = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(outs, out.detach())
+        assert all(torch.equal(outs[0], t) for t in outs)  # replicated result, bit for bit
     finally:
         dist.destroy_process_group()
 

@@ -69,3 +69,40 @@ def test_two_ranks_agree_on_the_assignment(tmp_path):
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     a, b = (np.load(tmp_path / f"ids_{r}.npy") for r in range(world))
     assert np.array_equal(a, b)
+
+
+def _gather_worker(rank, world, port):
+    sys.path.insert(0, str(ROOT))
+    from compressgnn_b200 import dist as cdist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        gen = torch.Generator().manual_seed(3)  # the full problem on every rank
+        full = torch.randn(6, 8, generator=gen, dtype=torch.float64)
+        weight = torch.randn(10, 8, generator=gen, dtype=torch.float64)
+        target = torch.randn(6, 10, generator=gen, dtype=torch.float64)
+        ref_in = full.clone().requires_grad_()
+        ((ref_in @ weight.t() - target) ** 2).sum().backward()
+        begin, end = cdist.column_range(8, rank, world)
+        # (a) every rank consumes the gathered matrix for its own slice of the outputs
+        local = full[:, begin:end].clone().requires_grad_()
+        gathered = cdist.gather_columns_autograd(local, None, replicated_consumer=False)
+        assert torch.equal(gathered, full)
+        ob, oe = cdist.column_range(10, rank, world)
+        ((gathered @ weight[ob:oe].t() - target[:, ob:oe]) ** 2).sum().backward()
+        torch.testing.assert_close(local.grad, ref_in.grad[:, begin:end])
+        # (b) every rank computes all outputs: the gradient arrives whole, no reduction
+        local = full[:, begin:end].clone().requires_grad_()
+        gathered = cdist.gather_columns_autograd(local, None, replicated_consumer=True)
+        ((gathered @ weight.t() - target) ** 2).sum().backward()
+        torch.testing.assert_close(local.grad, ref_in.grad[:, begin:end])
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_differentiable_column_gather_on_two_ranks():
+    """The gather in front of the Linear of a column-sharded layer: forward is the concatenation,
+    backward sums over ranks when the consumers differ and only slices when they are replicas."""
+    world, port = 2, _free_port()
+    mp.spawn(_gather_worker, args=(world, port), nprocs=world, join=True)
