@@ -214,6 +214,7 @@ def run_gpu(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep NCCL's banner off stdout (one JSON line)
         dist.init_process_group("nccl", device_id=device)
 
     wl = dict(WORKLOADS[args.workload])
@@ -532,6 +533,7 @@ def run_gcn(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep NCCL's banner off stdout (one JSON line)
         dist.init_process_group("nccl", device_id=device)
     data, e_orig = build_graph("propagation")
     graph = data.edge_index

@@ -36,6 +36,12 @@
 #ifndef CGNN_SEG_PREFETCH
 #define CGNN_SEG_PREFETCH 1    // request the next (source,value) batch before consuming the current
 #endif
+#ifndef CGNN_SEG_FFMA2
+#define CGNN_SEG_FFMA2 0    // packed fma.rn.f32x2 in the row update: measured slower (148 -> 213 us at F=128)
+#endif
+#ifndef CGNN_SEG_VEC_META
+#define CGNN_SEG_VEC_META 1 // a stage's value words read as 16-byte vectors instead of one by one
+#endif
 #ifndef CGNN_SEG_THREADS
 #define CGNN_SEG_THREADS 128
 #endif
@@ -155,7 +161,7 @@ __device__ __forceinline__ void fma_row(Vec<T, VW> (&acc)[VPL], const Vec<T, VW>
 #pragma unroll
     for (int p = 0; p < VPL; ++p) {
         if (colok[p]) {
-            if constexpr (sizeof(T) == 4 && VW == 4) {
+            if constexpr (CGNN_SEG_FFMA2 && sizeof(T) == 4 && VW == 4) {
                 // two packed fma.rn.f32x2 (sm_100): each half is the IEEE fma of the scalar form
                 const float2 ww = make_float2(w, w);
                 const float2 lo = __ffma2_rn(make_float2(x[p].v[0], x[p].v[1]), ww, make_float2(acc[p].v[0], acc[p].v[1]));
@@ -724,6 +730,7 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
         // the stage moves to registers and is handed back for refilling before the arithmetic
         V x[B][VPL];
         T w[B];
+#if CGNN_SEG_VEC_META
         static_assert(B % VW == 0, "a stage's value words are read as whole vectors");
 #pragma unroll
         for (int j = 0; j < B; j += VW) {
@@ -731,6 +738,10 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
 #pragma unroll
             for (int i = 0; i < VW; ++i) w[j + i] = wv.v[i];
         }
+#else
+#pragma unroll
+        for (int j = 0; j < B; ++j) w[j] = meta[st * B + j];
+#endif
 #pragma unroll
         for (int j = 0; j < B; ++j) {
 #pragma unroll
