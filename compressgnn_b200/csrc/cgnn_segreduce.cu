@@ -45,6 +45,16 @@
 #ifndef CGNN_SEG_THREADS
 #define CGNN_SEG_THREADS 128
 #endif
+#ifndef CGNN_SEG_OUT_HINT
+#define CGNN_SEG_OUT_HINT 0   // finished rows: 0 plain store, 1 streaming store (st.cs), 2 L2 evict-first policy
+#endif
+#ifndef CGNN_SEG_LOAD_HINT
+#define CGNN_SEG_LOAD_HINT 0  // staged rows: 0 no hint, 1 all evict-last, 2 near evict-last / far evict-first,
+                              // 3 near evict-last / far no hint, 4 all evict-first
+#endif
+#ifndef CGNN_SEG_NEAR_WINDOW
+#define CGNN_SEG_NEAR_WINDOW 4096
+#endif
 #ifndef CGNN_SEG_MINBLOCKS
 #define CGNN_SEG_MINBLOCKS 6
 #endif
@@ -78,6 +88,27 @@ __device__ __forceinline__ Vec<T, VW> gather_load(const T *p) {
     return r;
 #else
     return vec_load<T, VW>(p);
+#endif
+}
+
+// Store of a finished output row (written once, never read again by the launch).
+template <typename T, int VW>
+__device__ __forceinline__ void row_store(T *p, const Vec<T, VW> &x) {
+#if CGNN_SEG_OUT_HINT == 1
+    vec_store_cs<T, VW>(p, x);
+#elif CGNN_SEG_OUT_HINT == 2
+    if constexpr (sizeof(T) * VW == 16) {
+        uint64_t pol;
+        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+        const float4 t = *reinterpret_cast<const float4 *>(&x);
+        asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(p), "f"(t.x), "f"(t.y), "f"(t.z),
+                     "f"(t.w), "l"(pol)
+                     : "memory");
+    } else {
+        vec_store_cs<T, VW>(p, x);
+    }
+#else
+    vec_store<T, VW>(p, x);
 #endif
 }
 
@@ -214,7 +245,7 @@ __device__ __forceinline__ void finish_row(const SegArgs<T> &a, int32_t row, int
 #pragma unroll
                 for (int i = 0; i < VW; ++i) r.v[i] = r.v[i] / divisor;
             }
-            vec_store<T, VW>(orow + p * (LPR * VW), r);
+            row_store<T, VW>(orow + p * (LPR * VW), r);
         }
     }
 }
@@ -594,6 +625,15 @@ __device__ __forceinline__ void bulk_copy_to_shared(void *dst, const void *src, 
                  : "memory");
 }
 
+__device__ __forceinline__ void bulk_copy_to_shared_hint(void *dst, const void *src, uint32_t bytes, uint64_t *bar,
+                                                         uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            shared_addr(dst)),
+        "l"(src), "r"(bytes), "r"(shared_addr(bar)), "l"(policy)
+        : "memory");
+}
+
 template <typename T, int VPL, bool MASKED>
 struct BulkLayout {
     static constexpr int SLOT = 32 * VPL * 16;  // bytes of one staged row tile
@@ -684,6 +724,12 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
         o_next = a.entries[e_begin + 32 + lane];
         if (a.val) v_next = a.val[e_begin + 32 + lane];
     }
+#if CGNN_SEG_LOAD_HINT
+    uint64_t pol_last, pol_first;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_last));
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_first));
+    const int32_t unit_row = item_index >= 0 ? (int32_t)-0x40000000 : __shfl_sync(FULL, myrow, 0);
+#endif
     int window = 0;
     auto issue = [&](int b) {
         const int first = b * B;  // position of the stage's first entry in the unit's stream
@@ -705,8 +751,30 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
         if (j >= 0 && j < cnt) {
             const int64_t off = (int64_t)(o & 0x7fffffff) * width + col0;
             meta[st * B + j] = v;
+#if CGNN_SEG_LOAD_HINT == 1
+            bulk_copy_to_shared_hint(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off, slot_bytes,
+                                     &bars[st], pol_last);
+#elif CGNN_SEG_LOAD_HINT == 4
+            bulk_copy_to_shared_hint(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off, slot_bytes,
+                                     &bars[st], pol_first);
+#elif CGNN_SEG_LOAD_HINT == 2 || CGNN_SEG_LOAD_HINT == 3
+            {
+                const int32_t dist = (o & 0x7fffffff) - unit_row;
+                const bool near = o >= 0 || (dist >= -CGNN_SEG_NEAR_WINDOW && dist <= CGNN_SEG_NEAR_WINDOW);
+                if (near)
+                    bulk_copy_to_shared_hint(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off,
+                                             slot_bytes, &bars[st], pol_last);
+                else if (CGNN_SEG_LOAD_HINT == 2)
+                    bulk_copy_to_shared_hint(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off,
+                                             slot_bytes, &bars[st], pol_first);
+                else
+                    bulk_copy_to_shared(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off,
+                                        slot_bytes, &bars[st]);
+            }
+#else
             bulk_copy_to_shared(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off, slot_bytes,
                                 &bars[st]);
+#endif
             if constexpr (MASKED)
                 bulk_copy_to_shared(ring + (size_t)(st * PARTS * B + B + j) * SLOT, a.mask_src + off, slot_bytes,
                                     &bars[st]);
