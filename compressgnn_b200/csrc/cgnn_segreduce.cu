@@ -20,7 +20,7 @@
 
 #include "cgnn_plan.h"
 
-// Build-time tuning knobs (defaults are the measured best; see profiles/).
+// Build-time tuning knobs (the defaults are the measured best on B200).
 #ifndef CGNN_SEG_USCALE
 #define CGNN_SEG_USCALE 8   // 16-byte gather loads a lane keeps in flight
 #endif
@@ -840,10 +840,15 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
         }
     }
     if (expired) {
-        // give up on this unit: record it, let the copies still in flight land (bounded), write nothing
+        // give up on this unit: record it and let the copies still in flight land (bounded).  Rows of a
+        // direct unit stay unwritten; a chunk still publishes a (zero) partial sum and draws its ticket, so
+        // that the row's ticket word returns to zero for the next launch.  Either way the status word
+        // tells the host that this launch's output is not to be used.
         if (lane == 0) atomicOr(&g_seg_status, STATUS_WAIT_EXPIRED);
         for (int bb = b + 1; bb < nb && bb < b + S; ++bb) mbar_wait_bounded(&bars[bb % S], (uint32_t)(bb / S) & 1u);
-        return;
+        if (item_index < 0) return;
+#pragma unroll
+        for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
     }
     if (item_index < 0) {
         while (cur < nr) flush();
@@ -921,7 +926,7 @@ template <typename T, int VW, int LPR, int VPL, bool MASKED, bool GENERIC>
 static int launch_cfg(const SegArgs<T> &a, cudaStream_t stream) {
     constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR - 1;
     const int64_t units = ceil_div(a.n_direct, RPU) + a.n_items;
-    const int64_t per_block = (CGNN_SEG_NARROW_THREADS / 32) * (32 / LPR);
+    const int64_t per_block = (CGNN_SEG_THREADS / 32) * (32 / LPR);
     const int64_t gx = ceil_div(units, per_block);
     const int64_t gy = ceil_div(a.width, (int64_t)LPR * VPL * VW);
     CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
@@ -1103,10 +1108,11 @@ static int colsum(const T *x, int64_t rows, int64_t width, T *part, T *out, cuda
 // ---------------------------------------------------------------------------------------
 __global__ void scatter_entries_kernel(const int32_t *rowptr, const int32_t *col, const int32_t *dst,
                                        const int32_t *lead, int64_t rows, int term, int32_t value_base,
-                                       int32_t *entries, int32_t *vperm) {
+                                       int32_t *entries, int32_t *vperm, int32_t *max_source) {
     // one warp per row; `lead` holds the row's term-0 length when this is term 1
     const int lane = threadIdx.x & 31;
     const int64_t warps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    int32_t largest = -1;  // largest source row this thread has seen
     for (int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
         const int b = rowptr[r], e = rowptr[r + 1];
         if (b == e) continue;
@@ -1114,10 +1120,14 @@ __global__ void scatter_entries_kernel(const int32_t *rowptr, const int32_t *col
         for (int k = b + lane; k < e; k += 32) {
             const int32_t cv = col[k];
             if (cv < 0) atomicOr(&g_seg_status, STATUS_BAD_CSR);
+            largest = max(largest, cv);
             entries[d + (k - b)] = cv | (term ? (int32_t)0x80000000 : 0);
             if (vperm) vperm[d + (k - b)] = value_base + k;
         }
     }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) largest = max(largest, __shfl_xor_sync(0xffffffffu, largest, m));
+    if (lane == 0 && largest >= 0) atomicMax(&max_source[term], largest);
 }
 
 template <typename T>
@@ -1213,7 +1223,8 @@ int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *cons
     const size_t o_items = o_urow + span(urow.size() * 4);
     const size_t o_longs = o_items + span(items.size() * 16);
     const size_t o_dst = o_longs + span(longs.size() * 16);
-    const size_t staged = o_dst + span(dst.size() * 4);
+    const size_t o_maxsrc = o_dst + span(dst.size() * 4);  // largest source row of each term, filled by the scatter
+    const size_t staged = o_maxsrc + span(2 * 4);
     const size_t o_entries = staged;
     const size_t o_vperm = o_entries + span((size_t)total * 4);
     const size_t bytes = o_vperm + (want_vperm ? span((size_t)total * 4) : 0);
@@ -1224,6 +1235,8 @@ int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *cons
     put(o_items, items.data(), items.size() * 16);
     put(o_longs, longs.data(), longs.size() * 16);
     put(o_dst, dst.data(), dst.size() * 4);
+    int32_t max_source[2] = {-1, -1};
+    put(o_maxsrc, max_source, sizeof(max_source));
     // Stream-ordered allocation: an assignment refresh builds and drops a plan every few epochs,
     // and cudaMalloc / cudaFree would each stall the whole device.
     p->home = stream;
@@ -1252,12 +1265,15 @@ int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *cons
             if (p->nnz[t] == 0) continue;
             scatter_entries_kernel<<<blocks, 256, 0, stream>>>(rowptr[t], col[t], dst_dev, t ? rowptr[0] : nullptr,
                                                                rows, t, t ? (int32_t)p->nnz[0] : 0, p->entries,
-                                                               p->vperm);
+                                                               p->vperm, reinterpret_cast<int32_t *>(base + o_maxsrc));
         }
         CGNN_LAUNCH_CHECK();
+        CGNN_CUDA(cudaMemcpyAsync(max_source, base + o_maxsrc, sizeof(max_source), cudaMemcpyDeviceToHost, stream));
     }
     // the staged host buffer must outlive the copy
     CGNN_CUDA(cudaStreamSynchronize(stream));
+    p->source_rows[0] = (int64_t)max_source[0] + 1;
+    p->source_rows[1] = (int64_t)max_source[1] + 1;
     return CGNN_OK;
 }
 
@@ -1408,6 +1424,13 @@ int cgnn_plan_info(const cgnn_plan *p, int64_t info[8]) {
     info[5] = p->n_direct;
     info[6] = p->nterms;
     info[7] = p->compact;
+    return CGNN_OK;
+}
+
+int cgnn_plan_source_rows(const cgnn_plan *p, int64_t rows[2]) {
+    CGNN_REQUIRE(p != nullptr && rows != nullptr, "plan source rows: null argument");
+    rows[0] = p->source_rows[0];
+    rows[1] = p->source_rows[1];
     return CGNN_OK;
 }
 

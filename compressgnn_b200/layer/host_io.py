@@ -83,5 +83,7 @@ class HostPropagation:
         return self._submit(_spmm._backward, grad_host, grad_in_host)
 
     def synchronize(self):
-        """Block until every queued pass has delivered its host result."""
+        """Block until every queued pass has delivered its host result; raises if a kernel
+        recorded a problem (bad index, a staged copy that never arrived) along the way."""
         self._down.synchronize()
+        _native.raise_on_device_status()

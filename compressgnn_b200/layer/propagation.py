@@ -1,12 +1,14 @@
 """Module wrappers around the compressed propagation (ref: ``layer/CompressgnnPropagation.py``
-:62-85, ``layer/KPropagate.py:12-27``, ``layer/KPUPropagate.py:9-37``).  Only the
-``CompressGraph`` (CSR / SpMM) form of ``edge_index`` is served here."""
+:62-85, ``layer/KPropagate.py:12-27``, ``layer/KPUPropagate.py:9-37``).  ``edge_index`` is either
+a ``CompressGraph`` (the CSR / SpMM form) or the list of per-phase edge tensors of the COO form;
+both end in the same segment-reduce kernels."""
 from typing import Optional
 
 import torch
 from torch import Tensor
 
 from ..loader.compress_graph import CompressGraph
+from .phased import phased_propagate
 from .spmm import Compressgnn_SPMM
 
 AGGRS = {'add', 'sum', 'mean', 'min', 'max', 'mul'}
@@ -24,10 +26,14 @@ class Propagate(torch.nn.Module):
 
     def compressgnn_propagate(self, x: Tensor, edge_index, edge_weight=None, size=None,
                               vertex_cnt: int = None, rule_cnt: int = None):
-        if not isinstance(edge_index, CompressGraph):
-            raise NotImplementedError("only CompressGraph (graph_type='csr') inputs are supported; the "
-                                      "per-level COO scatter form is not part of compressgnn_b200")
-        return self.update(self.SPMM(edge_index=edge_index, x_j=x))
+        if isinstance(edge_index, CompressGraph):
+            return self.update(self.SPMM(edge_index=edge_index, x_j=x))
+        if isinstance(edge_index, (list, tuple)) and (len(edge_index) == 0 or torch.is_tensor(edge_index[0])):
+            # the per-phase edge lists of CompressgnnData(graph_type="coo") (ref :68-83)
+            if self.aggr not in ('add', 'sum'):
+                raise ValueError("the phased edge-list propagation sums its messages (aggr='add')")
+            return self.update(phased_propagate(x, edge_index, edge_weight, vertex_cnt, rule_cnt))
+        raise TypeError("edge_index must be a CompressGraph or the list of per-phase [2, E] edge tensors")
 
     def update(self, out: Tensor) -> Tensor:
         return out

@@ -62,6 +62,9 @@ class SegmentPlan:
         check(lib().cgnn_plan_info(handle, info))
         (self.rows, self.nnz, self.split, self.long_rows, self.chunks, self.direct_units,
          self.terms, self.compact_rows) = [int(v) for v in info]
+        need = (ctypes.c_int64 * 2)()
+        check(lib().cgnn_plan_source_rows(handle, need))
+        self.source_rows = (int(need[0]), int(need[1]))  # rows each source matrix must have
 
     @property
     def handle(self):
@@ -216,6 +219,8 @@ def spmm_with_plan(plan, value, mat, out=None, accumulate=False):
         return out
     if plan.nnz == 0:
         return out if accumulate else out.zero_()
+    _require(mat.size(0) >= plan.source_rows[0],
+             f"spmm: the index array refers to row {plan.source_rows[0] - 1} but mat has {mat.size(0)} rows")
     sp, sb = plan.scratch(width, code)
     if value is not None:
         value = plan.values(value)
@@ -246,6 +251,10 @@ def spmm_pair_with_plan(plan, value0, mat0, value1, mat1, out=None, accumulate=F
         accumulate = False
     if out.numel() == 0:
         return out
+    for which, mat in enumerate((mat0, mat1)):
+        _require(mat.size(0) >= plan.source_rows[which],
+                 f"spmm_pair: block {which} refers to row {plan.source_rows[which] - 1} but its matrix has "
+                 f"{mat.size(0)} rows")
     sp, sb = plan.scratch(width, code)
     value = plan.values(value0, value1)
     with torch.cuda.device(mat0.device):
@@ -268,7 +277,9 @@ def spmm_func(vlist, elist, value, mat, method, optional_out=None):
     _require(mat.is_contiguous(), "mat must be contiguous")
     if optional_out is not None:
         _require(optional_out.is_cuda, "optional_out must be GPU tensor")
-        out = optional_out.contiguous()
+        # accumulated in place and returned: a silent contiguous copy would break that contract
+        _require(optional_out.is_contiguous(), "optional_out must be contiguous")
+        out = optional_out
     else:
         sizes = list(mat.shape)
         sizes[0] = vlist.size(-1) - 1
@@ -515,3 +526,16 @@ def device_status():
     status = ctypes.c_int(0)
     check(lib().cgnn_device_status(ctypes.byref(status)))
     return int(status.value)
+
+
+_STATUS_BITS = ((1, "an index outside its table was skipped"),
+                (2, "a bounded wait on a staged copy ran out: that launch's output is not to be used"),
+                (4, "a CSR array held a negative or over-wide index"))
+
+
+def raise_on_device_status():
+    """``device_status()`` turned into an exception: raises RuntimeError naming the bits that were set."""
+    status = device_status()
+    if status:
+        what = "; ".join(text for bit, text in _STATUS_BITS if status & bit)
+        raise RuntimeError(f"compressgnn_b200 device status {status}: {what}")

@@ -31,7 +31,9 @@ const char *cgnn_last_error(void);
 
 /* OR of the status bits recorded by kernels since the last call (1 = an index outside its
  * range was met and skipped, 2 = a bounded wait ran out, 4 = malformed CSR); clears the
- * word.  Synchronises the device.  The reference traps the GPU on a bad index instead
+ * word.  Synchronises the device.  When bit 2 is set, the output of the launch that set it is
+ * undefined (rows of the unit that gave up were not written); every launch still leaves the
+ * plan's ticket words zero.  The reference traps the GPU on a bad index instead
  * (ref: src/runtime/csrc/cluster/cuda/cluster_kernel.cu:66,82,92,104). */
 int cgnn_device_status(int *status_out);
 
@@ -66,6 +68,12 @@ void cgnn_plan_destroy(cgnn_plan *plan);
 /* info[0..7] = rows, entries (both terms), split, long rows, chunks, rows in the direct
  * list, terms, 1 if empty rows are left out of the list. */
 int cgnn_plan_info(const cgnn_plan *plan, int64_t info[8]);
+
+/* rows[t] = 1 + the largest source row that block t of the plan refers to (0 when the block has
+ * no entries).  The SpMM entry points take raw pointers and cannot see how many rows `src`
+ * has: a caller passes only matrices with at least this many rows.  (The reference's kernels
+ * index `mat` with elist unchecked, src/runtime/csrc/sparse/cuda/row_balance.cuh:82-128.) */
+int cgnn_plan_source_rows(const cgnn_plan *plan, int64_t rows[2]);
 
 /* A plan keeps its entries in its own order (short rows back to back, then the chunks of
  * long rows; for two blocks a row's entries of block 0 precede those of block 1).  This
@@ -106,8 +114,11 @@ int cgnn_spmm(const cgnn_plan *plan, int dtype, int64_t width, const void *val,
  *
  * Same result as cgnn_spmm (bit for bit).  The call allocates nothing -- no cudaMalloc,
  * cudaFree or allocating library routine.  Limits and rules:
- *   - plans whose chunk partial sums for `width` do not fit in CGNN_STATIC_SCRATCH_BYTES
- *     (cgnn_plan_scratch_bytes tells) are rejected with CGNN_ERR_INVALID and a message;
+ *   - a plan is accepted when cgnn_plan_ticket_bytes(plan, width, dtype) + chunks * width *
+ *     sizeof(element) <= CGNN_STATIC_SCRATCH_BYTES, with chunks = info[4] of cgnn_plan_info;
+ *     anything larger is rejected with CGNN_ERR_INVALID and a message.  (cgnn_plan_scratch_bytes
+ *     is an upper bound of that sum: it also counts alignment padding and the bias-gradient
+ *     stage this entry point does not use);
  *   - the buffer is shared by every call on a device and keeps the previous call's contents;
  *     each call clears the ticket words it needs itself, but two calls that overlap on the
  *     GPU (different streams, no dependency) race on it -- order them;

@@ -236,3 +236,29 @@ def reference_modules():
                 mod = None
         mods.append(mod)
     return tuple(mods)
+
+
+def reference_propagation(blocks, x, grad, n, r, threads=None):
+    """One forward and one backward compressed propagation on the CPU by the strongest checker at
+    hand: the reference's own compiled ``spmm_func(..., "rowbalance", ...)`` chained in the order
+    of layer/CompressgnnSPMM.py:47-53 (forward) and :80-85 (backward) when ``oracle/_ref`` is
+    present, else this module's C restatement.  ``blocks`` as for ``propagate_forward``.
+    Returns ``(out, grad_in, kind)`` as numpy arrays with ``kind`` "reference" or "port"."""
+    rt, _off = reference_modules()
+    if rt is None:
+        return propagate_forward(blocks, x), propagate_backward(blocks, grad, n, r), "port"
+    import os
+    import torch
+    torch.set_num_threads(threads or os.cpu_count() or 1)
+    t = lambda blk: tuple(torch.from_numpy(np.ascontiguousarray(a)) for a in blk)
+    spmm_ref = lambda blk, m, out=None: rt.spmm_func(blk[0], blk[1], blk[2], m, "rowbalance", out)
+    xt, gt = torch.from_numpy(np.ascontiguousarray(x)), torch.from_numpy(np.ascontiguousarray(grad))
+    rule = spmm_ref(t(blocks["r2v"]), xt)
+    for level in blocks["r2r"]:
+        rule = spmm_ref(t(level), rule, rule)
+    out = spmm_ref(t(blocks["v2v"]), xt, spmm_ref(t(blocks["v2r"]), rule))
+    rule_g = spmm_ref(t(transpose_csr(*blocks["v2r"], r)), gt)
+    for level in reversed(blocks["r2r"]):
+        rule_g = spmm_ref(t(transpose_csr(*level, r)), rule_g, rule_g)
+    gx = spmm_ref(t(transpose_csr(*blocks["r2v"], n)), rule_g, spmm_ref(t(transpose_csr(*blocks["v2v"], n)), gt))
+    return out.numpy(), gx.numpy(), "reference"

@@ -261,6 +261,33 @@ def test_gcn_with_both_compressions_trains_one_step():
     assert model.layers[0].cluster.refresh_count == 1  # reused at epoch 1
 
 
+def test_k_fold_propagation_with_cache():
+    """KPUPropagate (ref: layer/KPUPropagate.py:25-37): K propagations in a row, and with
+    cached=True the first result is kept and handed back detached whatever comes in later."""
+    from compressgnn_b200.layer import KPUPropagate
+    data = make_data(width=24)
+    blocks = oracle_blocks(data.edge_index)
+    data.to("cuda")
+    x = data.x.clone().requires_grad_()
+    twice = KPUPropagate(K=2)
+    out = twice(x, data.edge_index, None, data.vertex_cnt, data.rule_cnt)
+    ref = oracle.propagate_forward(blocks, oracle.propagate_forward(blocks, data.x.cpu().numpy()))
+    assert_close_rel(out.detach().cpu().numpy(), ref, what="two propagations")
+    (gx,) = torch.autograd.grad(out, x, torch.ones_like(out))
+    ones = np.ones_like(ref)
+    n, r = data.vertex_cnt, data.rule_cnt
+    assert_close_rel(gx.cpu().numpy(), oracle.propagate_backward(blocks, oracle.propagate_backward(blocks, ones, n, r), n, r),
+                     what="gradient through two propagations")
+    assert twice(2 * x, data.edge_index, None, n, r).data_ptr() != out.data_ptr()  # no cache unless asked for
+    cached = KPUPropagate(K=2, cached=True)
+    first = cached(x, data.edge_index, None, n, r)
+    second = cached(torch.zeros_like(x), data.edge_index, None, n, r)
+    assert torch.equal(first, second) and not second.requires_grad
+    cached.reset_cache()
+    assert not cached(torch.zeros_like(x), data.edge_index, None, n, r).any()
+    assert repr(cached) == "KPUPropagate(K=2)"
+
+
 @pytest.mark.parametrize("depth", [1, 2, 3])
 def test_host_propagation_queue_matches_resident_passes(depth):
     """Passes queued on host matrices (upload / propagate / download streams over a ring of

@@ -145,6 +145,29 @@ def test_spmm_empty_and_errors(rt):
     assert rt.device_status() == 0
 
 
+def test_sources_and_outputs_are_checked_on_the_host(rt):
+    """A matrix with fewer rows than the index array names, and an output that could not be
+    accumulated in place, are refused before anything is launched."""
+    rowptr = cu(np.array([0, 2, 3], np.int64))
+    col = cu(np.array([0, 6, 2], np.int64))
+    val = torch.ones(3, device="cuda")
+    plan = rt.SegmentPlan.from_csr(rowptr, col)
+    assert plan.source_rows == (7, 0)
+    ok = rt.spmm_func(rowptr, col, val, torch.ones(7, 4, device="cuda"), "rowbalance_rowcache", None)
+    assert ok.cpu().tolist() == [[2.0] * 4, [1.0] * 4]
+    with pytest.raises(RuntimeError, match="refers to row 6"):
+        rt.spmm_func(rowptr, col, val, torch.ones(6, 4, device="cuda"), "rowbalance_rowcache", None)
+    pair = rt.SegmentPlan.from_csr(rowptr, col, cu(np.array([0, 1, 1], np.int64)), cu(np.array([9], np.int64)))
+    assert pair.source_rows == (7, 10)
+    with pytest.raises(RuntimeError, match="block 1 refers to row 9"):
+        rt.spmm_pair_with_plan(pair, val, torch.ones(7, 4, device="cuda"), torch.ones(1, device="cuda"),
+                               torch.ones(9, 4, device="cuda"))
+    strided = torch.zeros(2, 8, device="cuda")[:, ::2]
+    with pytest.raises(RuntimeError, match="contiguous"):
+        rt.spmm_func(rowptr, col, val, torch.ones(7, 4, device="cuda"), "rowbalance_rowcache", strided)
+    assert rt.device_status() == 0
+
+
 def test_fused_pair_matches_two_calls(rt):
     rng = np.random.default_rng(21)
     rows, n0, n1, width = 700, 400, 650, 96
