@@ -1,5 +1,5 @@
-"""Benchmark of the compressed-propagation hot path (and, on request, of the cluster /
-reconstruct operators) on synthetic inputs.
+"""Benchmark of the compressed-propagation hot path (and of the cluster / reconstruct operators
+and the GCN epoch around it) on synthetic inputs.
 
     python bench.py --gpus N --steps K --warmup W            # this package, N GPUs (torchrun for N>1)
     python bench.py --impl reference --steps K --warmup W    # the reference's own CPU operators
@@ -10,13 +10,16 @@ One step = one forward and one backward pass over the whole graph.  The metric i
 original-edge x feature products per second: 2 * E_orig * F / t_step.
 
 With N GPUs the feature columns are sharded and the graph replicated (no data-path collective).
-The default is weak scaling -- each GPU keeps a 256-column block, so the job's matrix is
-N x 256*gpus; `--scaling strong` divides the 256 columns instead.
+The default is strong scaling -- the workload's 256 columns are divided among the GPUs, the job is
+the same at every N; `--scaling weak` gives every GPU a full 256-column block instead.
 
 Prints ONE JSON line (rank 0).  `value` is device-resident throughput (CUDA events, max over
 ranks); `e2e` goes through the public host-buffer front end with pinned host matrices, copies included;
 `roofline` is for the dominant kernel (the fused vertex pass of the forward); `cpu_baseline`
-is the reference's CPU spmm_func chain on this host's cores.
+is the reference's CPU spmm_func chain on this host's cores, and `parity_checked` compares the
+GPU's forward and backward results with that chain's on the same inputs.  `extra` carries short
+legs of the other two operator groups: the cluster / reconstruct operators at 2.45 M nodes and
+the 2-layer GCN epoch over four feature widths (sharded over the GPUs when N > 1).
 """
 import argparse
 import json
@@ -47,9 +50,34 @@ WORKLOADS = {
     "propagation-xl": dict(n=18500000, x_min=8.6, width=128, seed=4),
 }
 COMPRESS = dict(min_pair_frequency=4, threshold=4, max_depth=3, min_edge=1000000)
-# dram__bytes_read.sum + dram__bytes_write.sum of one forward fused vertex pass at N=1, from the
-# ncu capture summarised in profiles/seg_bulk_kernel_fused_vertex_pass_config2.md (same workload).
-NCU_TRAFFIC_BYTES = {("propagation", 1): 1.461e9}
+TRAFFIC_RECORD = ROOT / "profiles" / "ncu_traffic.json"
+KERNEL_SOURCES = ("compressgnn_b200/csrc/cgnn_segreduce.cu", "compressgnn_b200/csrc/cgnn_common.cuh",
+                  "compressgnn_b200/csrc/cgnn_plan.h")
+
+
+def kernel_source_hash():
+    """sha256 over the sources the segment kernels are built from (ties a recorded ncu figure to
+    the code it was captured from)."""
+    import hashlib
+    h = hashlib.sha256()
+    for rel in KERNEL_SOURCES:
+        h.update((ROOT / rel).read_bytes())
+    return h.hexdigest()
+
+
+def recorded_traffic(workload, width, world):
+    """DRAM bytes (read + write) of one launch of the dominant kernel from the committed ncu
+    capture, or (None, why) when no capture matches this workload and the current kernel sources."""
+    if world != 1:
+        return None, "captured on one GPU only"
+    if not TRAFFIC_RECORD.is_file():
+        return None, "no ncu capture recorded"
+    for rec in json.loads(TRAFFIC_RECORD.read_text())["captures"]:
+        if rec["workload"] == workload and rec["feature_width"] == width:
+            if rec["kernel_source_sha256"] != kernel_source_hash():
+                return None, "the kernel sources changed since the ncu capture of " + rec["captured"]
+            return rec["dram_bytes_per_launch"], "ncu capture of " + rec["captured"]
+    return None, "no ncu capture of this workload"
 
 
 def build_graph(name):
@@ -142,26 +170,73 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------------------------
+# Shared pieces of the two arms
+# ---------------------------------------------------------------------------------------------
+def measured_peak():
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    if peaks_path.is_file():
+        return json.loads(peaks_path.read_text())["hbm_gbs"], "measured (MEASURED_PEAKS.json)"
+    return 6650.0, "fallback"
+
+
+def workload_config(name, data, e_orig, width_total, width, world, scaling):
+    """The `config` object of the JSON line: the same dict from both arms."""
+    g = data.edge_index
+    return {"workload": f"{name}: compressed propagation SpMM fwd+bwd, copying-model web graph",
+            "nodes": g.vertex_cnt, "orig_edges": e_orig, "compressed_edges": g.edge_count(),
+            "rules": g.rule_cnt, "levels": g.step, "feature_width": width_total,
+            "columns_per_gpu": width, "compressor": COMPRESS,
+            "l2": "inputs larger than L2 (X is %.0f MB per GPU)" % (4e-6 * g.vertex_cnt * width),
+            "parallelism": f"feature columns sharded over {world} GPU(s) ({scaling} scaling), graph replicated, "
+                           "no collective"}
+
+
+def widths_for(args, world):
+    """(columns of the whole job, columns of one GPU)."""
+    base = args.width or WORKLOADS[args.workload]["width"]
+    if args.scaling == "weak":
+        return base * world, base
+    assert base % world == 0, "feature width must divide by the number of GPUs"
+    return base, base // world
+
+
+def host_inputs(n, width, seed):
+    """Features and upstream gradient, drawn on the host so that the CPU and the GPU legs of one
+    run can be given the same numbers."""
+    import torch
+    gen = torch.Generator().manual_seed(seed)
+    return torch.randn(n, width, generator=gen), torch.randn(n, width, generator=gen)
+
+
+def scaled_error(actual, expected):
+    """max |a - b| / max(|b|, rms(row of b), rms(b)): the parity tests' bar for this is 1e-5 in fp32."""
+    import torch
+    a, b = actual.double(), expected.double()
+    scale = torch.maximum(torch.maximum(b.abs(), b.pow(2).mean(dim=1, keepdim=True).sqrt()), b.pow(2).mean().sqrt())
+    return float(((a - b).abs() / (scale + 1e-30)).max())
+
+
+# ---------------------------------------------------------------------------------------------
 # Reference CPU arm / CPU baseline
 # ---------------------------------------------------------------------------------------------
-def cpu_propagation(data, width, steps, warmup, seed=0):
+def cpu_propagation(data, x, grad, steps, warmup):
     """The reference's CPU path: spmm_func(..., "rowbalance", ...) chained in the order of
-    layer/CompressgnnSPMM.py:47-53 (forward) and :80-85 (backward), all host threads.
-    Returns (seconds per step, kind, cores, sample description)."""
+    layer/CompressgnnSPMM.py:47-53 (forward) and :80-85 (backward), all host threads, on the host
+    tensors `x` and `grad`.  Without the compiled reference the single-thread C restatement runs
+    on the first 8 columns and the time is scaled.
+    Returns (seconds per step, kind, cores, sample description, (out, grad_in) of the last step)."""
     import torch
     from oracle import oracle
     rt, _off = oracle.reference_modules()
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     g = data.edge_index
-    n, r = g.vertex_cnt, g.rule_cnt
-    gen = torch.Generator().manual_seed(seed)
+    width = x.size(1)
     if rt is not None:
         kind, sample_width = "reference", width
     else:
-        kind, sample_width, cores = "port", min(width, 8), 1  # scalar single-thread C port: a column slice
-    x = torch.randn(n, sample_width, generator=gen)
-    grad = torch.randn(n, sample_width, generator=gen)
+        kind, sample_width, cores = "port", min(width, 8), 1
+        x, grad = x[:, :sample_width].contiguous(), grad[:, :sample_width].contiguous()
     fwd_blocks = dict(r2v=g.r2v_graph.csr(), v2r=g.v2r_graph.csr(), v2v=g.v2v_graph.csr(),
                       levels=[lvl.csr() for lvl in g.r2r_graph])
     bwd_blocks = dict(v2r_t=g.v2r_graph.csc(), v2v_t=g.v2v_graph.csc(), r2v_t=g.r2v_graph.csc(),
@@ -191,61 +266,87 @@ def cpu_propagation(data, width, steps, warmup, seed=0):
         step()
     t0 = time.perf_counter()
     for _ in range(steps):
-        step()
+        result = step()
     dt = (time.perf_counter() - t0) / max(steps, 1)
     scale = width / sample_width  # a column slice scales linearly in the width
     sample = (f"full workload, {steps} steps" if sample_width == width else
               f"{sample_width} of {width} feature columns, {steps} steps, time scaled by {scale:g}")
-    return dt * scale, kind, cores, sample
+    return dt * scale, kind, cores, sample, result
 
 
 # ---------------------------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------------------------
-def run_gpu(args):
+def init_ranks():
     import torch
     import torch.distributed as dist
-    from compressgnn_b200.layer import Compressgnn_SPMM, spmm as spmm_layer
-    from compressgnn_b200 import runtime as rt
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if world > 1:
+    if world > 1 and not dist.is_initialized():
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep NCCL's banner off stdout (one JSON line)
         dist.init_process_group("nccl", device_id=device)
+    return world, rank, local_rank, device
 
-    wl = dict(WORKLOADS[args.workload])
-    if args.width:
-        wl["width"] = args.width
-    if args.scaling == "weak":
-        # every rank holds a full-width column block: the job's feature matrix is N x (F * world)
-        width = wl["width"]
-        width_total = width * world
-    else:
-        width_total = wl["width"]
-        assert width_total % world == 0, "feature width must divide by the number of GPUs"
-        width = width_total // world  # column shard of this rank; the graph is replicated
-    data, e_orig = build_graph(args.workload)
-    cpu_graph_for_baseline = data if rank == 0 else None
+
+def build_graph_once(name, world, rank):
+    """Every rank needs the host graph.  The large workload takes minutes of host time to generate
+    and compress, so with several ranks rank 0 builds it and hands it over through a file in shared
+    memory instead of every rank repeating the work on the same cores."""
+    import torch
+    import torch.distributed as dist
+    if world == 1 or WORKLOADS[name]["n"] < 2_000_000:
+        return build_graph(name)
+    path = Path("/dev/shm") / f"cgnn_bench_{os.environ.get('MASTER_PORT', '0')}_{name}.pt"
+    if rank == 0:
+        built = build_graph(name)
+        torch.save(built, path)
+    dist.barrier()
+    if rank != 0:
+        built = torch.load(path, weights_only=False)
+    dist.barrier()
+    if rank == 0:
+        path.unlink()
+    return built
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from compressgnn_b200.layer import spmm as spmm_layer
+    from compressgnn_b200 import runtime as rt
+
+    world, rank, local_rank, device = init_ranks()
+    width_total, width = widths_for(args, world)
+    data, e_orig = build_graph_once(args.workload, world, rank)
     graph = data.edge_index
     n = graph.vertex_cnt
+    warmup = max(args.warmup, 3)
+    config = workload_config(args.workload, data, e_orig, width_total, width, world, args.scaling)
+
+    # Inputs come from the host at sizes a host matrix is reasonable for (the same numbers then go to
+    # the CPU leg); the 18.5 M-node workload draws them on the device.
+    from_host = 4 * n * width <= 2**30
+    if from_host:
+        x_host, grad_host = host_inputs(n, width, 1234 + rank)
+        x, grad = x_host.to(device), grad_host.to(device)
+    else:
+        gen = torch.Generator(device=device).manual_seed(1234 + rank)
+        x = torch.randn(n, width, device=device, generator=gen)
+        grad = torch.randn(n, width, device=device, generator=gen)
 
     # CPU baseline first (rank 0, N=1 only), while the graph blocks are still host tensors.
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        sec, kind, cores, sample = cpu_propagation(cpu_graph_for_baseline, width_total, args.cpu_steps, 1)
+    cpu = cpu_result = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and from_host:
+        sec, kind, cores, sample, cpu_result = cpu_propagation(data, x_host, grad_host, args.cpu_steps, 1)
         cpu = {"value": 2 * e_orig * width_total / sec / 1e9, "unit": UNIT, "cores": cores, "kind": kind,
                "sample": sample, "ms_per_step": sec * 1e3}
 
     fwd_bytes, bwd_bytes = propagation_bytes(graph, width)
     graph.to(device)
-    gen = torch.Generator(device=device).manual_seed(1234 + rank)
-    x = torch.randn(n, width, device=device, generator=gen)
-    grad = torch.randn(n, width, device=device, generator=gen)
-    plan = graph.propagation_plan()
+    graph.propagation_plan()
     launches_per_step = 2 * (2 + graph.step)
 
     def step(record=None):
@@ -253,7 +354,7 @@ def run_gpu(args):
         gx = spmm_layer._backward(graph, grad, record)
         return out, gx
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(warmup):
         step()
     torch.cuda.synchronize()
     if world > 1:
@@ -290,24 +391,37 @@ def run_gpu(args):
     launch_ms = {k: float(np.mean(v)) for k, v in per_launch.items()}
     bytes_by_name = dict(fwd_bytes + bwd_bytes)
 
+    # the GPU's results against the CPU leg's, same inputs (N=1)
+    parity = None
+    if cpu_result is not None:
+        out, gx = step()
+        cols = cpu_result[0].size(1)
+        err_f = scaled_error(out[:, :cols].cpu(), cpu_result[0])
+        err_b = scaled_error(gx[:, :cols].cpu(), cpu_result[1])
+        parity = {"against": f"cpu_baseline ({cpu['kind']}), same inputs, {cols} of {width} columns",
+                  "max_scaled_error_forward": err_f, "max_scaled_error_backward": err_b, "tolerance": 1e-5,
+                  "ok": bool(err_f <= 1e-5 and err_b <= 1e-5)}
+        del out, gx
+        assert parity["ok"], f"GPU and CPU results differ: {parity}"
+
     # end to end through the public host-buffer front end: pinned host operands, every upload
     # and download inside the timed region, passes queued so that the two copy directions overlap
     e2e_sec = e2e_sync_sec = None
-    if not args.no_e2e and 4 * n * width <= 4 * 2**30:  # four pinned copies of X: skipped for very large shards
+    if not args.no_e2e and from_host:
         from compressgnn_b200.layer import HostPropagation
         pipe = HostPropagation(graph, width)
-        x_host = x.cpu().pin_memory()
-        g_host = grad.cpu().pin_memory()
-        out_host = torch.empty_like(x_host).pin_memory()
-        gx_host = torch.empty_like(x_host).pin_memory()
+        x_pin = x_host.pin_memory()
+        g_pin = grad_host.pin_memory()
+        out_host = torch.empty_like(x_pin).pin_memory()
+        gx_host = torch.empty_like(x_pin).pin_memory()
 
         def e2e_steps(count, wait_each):
             if world > 1:
                 dist.barrier()
             t0 = time.perf_counter()
             for _ in range(count):
-                pipe.forward(x_host, out_host)
-                pipe.backward(g_host, gx_host)
+                pipe.forward(x_pin, out_host)
+                pipe.backward(g_pin, gx_host)
                 if wait_each:
                     pipe.synchronize()
             pipe.synchronize()
@@ -322,51 +436,63 @@ def run_gpu(args):
         e2e_sync_sec = e2e_steps(args.steps, True)   # each step waited for before the next is queued
         e2e_sec = e2e_steps(args.steps, False)       # steps queued back to back, one wait at the end
         assert torch.equal(out_host, step()[0].cpu()), "host front end and resident path disagree"
-        del pipe
+        del pipe, x_pin, g_pin, out_host, gx_host
 
-    status = rt.device_status()
-    assert status == 0, f"device status word {status}"
+    rt.raise_on_device_status()
+    del x, grad
+
+    # short legs of the other operator groups, after the timed region of the headline workload
+    extra = {}
+    if not args.no_extra and WORKLOADS[args.workload]["n"] < 2_000_000:
+        if world == 1:
+            extra["cluster"] = measure_cluster(args.cluster_nodes, max(3, min(args.steps, 10)), 3,
+                                               with_cpu=not args.no_cpu_baseline)
+        extra["gcn"] = measure_gcn(graph, e_orig, max(5, min(args.steps, 20)), 5, world, rank, device)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
         return
 
-    peaks_path = ROOT / "MEASURED_PEAKS.json"
-    if peaks_path.is_file():
-        peak, peak_src = json.loads(peaks_path.read_text())["hbm_gbs"], "measured (MEASURED_PEAKS.json)"
-    else:
-        peak, peak_src = 6650.0, "fallback"
+    peak, peak_src = measured_peak()
     dom = "fwd_out"
     achieved = bytes_by_name[dom] / (launch_ms[dom] * 1e-3) / 1e9
+    traffic, traffic_src = recorded_traffic(args.workload, width, world)
     work = 2 * e_orig * width_total
     line = {
         "metric": METRIC, "value": work / (ms_per_step * 1e-3) / 1e9, "unit": UNIT, "n_gpus": world,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: compressed propagation SpMM fwd+bwd, copying-model web graph",
-                   "nodes": n, "orig_edges": e_orig, "compressed_edges": graph.edge_count(),
-                   "rules": graph.rule_cnt, "levels": graph.step, "feature_width": width_total,
-                   "columns_per_gpu": width, "compressor": COMPRESS,
-                   "l2": "inputs larger than L2 (X is %.0f MB per GPU)" % (4e-6 * n * width),
-                   "parallelism": f"feature columns sharded over {world} GPU(s), graph replicated, no collective"},
+        "config": config,
         "e2e": ({"value": work / e2e_sec / 1e9, "unit": UNIT, "h2d_bytes_per_step": 2 * 4 * n * width,
                  "d2h_bytes_per_step": 2 * 4 * n * width, "ms_per_step": e2e_sec * 1e3,
                  "ms_per_step_waiting_each_step": e2e_sync_sec * 1e3,
+                 "host_GBps_all_ranks": 4 * 4 * n * width * world / e2e_sec / 1e9,
+                 "limit": "host memory / PCIe: every step moves the feature matrix and the result both ways",
                  "api": "HostPropagation.forward/backward on pinned host matrices"} if e2e_sec else None),
         "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "kernel": "seg_bulk_kernel (fused v2r+v2v vertex pass, forward)",
+        "roofline": {"bound": "hbm", "kernel": "fused v2r+v2v vertex pass of the forward (segment-reduce kernel)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_source": peak_src, "traffic": NCU_TRAFFIC_BYTES.get((args.workload, world)),
+                     "peak_source": peak_src, "traffic": traffic, "traffic_source": traffic_src,
                      "algorithmic_bytes_per_launch": bytes_by_name[dom], "ms_per_launch": launch_ms[dom],
                      "launches": {k: {"ms": launch_ms[k], "algorithmic_GBps": bytes_by_name[k] / launch_ms[k] / 1e6}
                                   for k in launch_ms}},
         "clocks": clocks.summary(),
     }
+    if world > 1 and args.scaling == "strong":
+        # what column sharding can give at best: feature bytes divide by N, the index stream does not
+        full = dict(fwd_bytes + bwd_bytes)
+        shard_bytes = sum(full.values())
+        index_bytes = 8 * graph.edge_count() * 2
+        one_gpu = (shard_bytes - index_bytes) * world + index_bytes
+        line["strong_scaling_ceiling_by_bytes"] = one_gpu / (world * shard_bytes)
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if parity is not None:
+        line["parity_checked"] = parity
+    if extra:
+        line["extra"] = extra
     print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
 
 
 def cpu_cluster(n, width, out_width, bits, fraction=8):
@@ -414,17 +540,16 @@ def cpu_cluster(n, width, out_width, bits, fraction=8):
             "sample": f"{m} of {n} nodes, {epochs} epochs with one refresh, time scaled by {fraction}"}
 
 
-def run_cluster(args):
+def measure_cluster(n, steps, warmup, with_cpu=True):
     """Config 3: Compressgnn_Cluster -> Linear(128->256) on representatives -> fused reconstruct
-    (bias + ReLU), forward + backward, 2.45 M nodes drawn from 4096 Gaussian centroids, H=16,
+    (bias + ReLU), forward + backward, `n` nodes drawn from 4096 Gaussian centroids, H=16,
     refresh_interval=5.  A step = one epoch.  Per-operator CUDA-event times and algorithmic GB/s
     are reported next to the epoch time; the CPU leg runs the reference's cluster_forward
-    plus the torch CPU formulas its layers use."""
+    plus the torch CPU formulas its layers use.  Returns the fields of a JSON line."""
     import torch
     from compressgnn_b200 import runtime as rt
     from compressgnn_b200.layer import Compressgnn_Cluster, Compressgnn_Reconstruct
-    torch.cuda.set_device(0)
-    n, width, out_width, bits = args.cluster_nodes, 128, 256, 16
+    width, out_width, bits = 128, 256, 16
     gen = torch.Generator(device="cuda").manual_seed(3)
     cent = torch.randn(4096, width, device="cuda", generator=gen)
     which = torch.randint(0, 4096, (n,), device="cuda", generator=gen)
@@ -444,19 +569,19 @@ def run_cluster(args):
         x.grad = None
         return y
 
-    for e in range(max(args.warmup, 3)):
+    for e in range(max(warmup, 3)):
         epoch(e)
     cluster.reset_cache()
     cluster.refresh_count = 0
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(0) as clocks:
+    with ClockSampler(torch.cuda.current_device()) as clocks:
         start.record()
-        for e in range(args.steps):
+        for e in range(steps):
             epoch(e)
         stop.record()
         torch.cuda.synchronize()
-    ms_epoch = start.elapsed_time(stop) / args.steps
+    ms_epoch = start.elapsed_time(stop) / steps
 
     # per-operator timings on the same tensors (CUDA events, median of 20)
     def timed(fn, reps_=20):
@@ -481,7 +606,7 @@ def run_cluster(args):
     g_small = torch.randn(groups, width, device="cuda", generator=gen)
     ops = {
         "cluster_assign (projection+codes+compaction)": (lambda: rt.cluster_assign(xd, cluster.random_vectors, bits, ws),
-                                                          4 * n * width + 4 * width * bits + 8 * n + 40 * n),
+                                                          4 * n * width + 4 * width * bits + 8 * n + 4 * 2**bits),
         "cluster_mean": (lambda: rt.cluster_mean(xd, ids, counts), 4 * n * width + 8 * n + 4 * groups * width),
         "cluster_mean_backward": (lambda: rt.cluster_mean_backward(g_small, ids, counts),
                                   4 * groups * width + 8 * n + 4 * n * width),
@@ -494,56 +619,131 @@ def run_cluster(args):
             lambda: rt.cluster_reconstruct_backward(grad_out, ids, y, groups, True, output_is_forward_result=True),
             4 * n * out_width + 8 * n + 8 * groups * out_width),
     }
-    peaks_path = ROOT / "MEASURED_PEAKS.json"
-    peak = json.loads(peaks_path.read_text())["hbm_gbs"] if peaks_path.is_file() else 6650.0
+    peak, peak_src = measured_peak()
     op_report = {}
     for name, (fn, nbytes) in ops.items():
         ms = timed(fn)
-        op_report[name] = {"ms": ms, "algorithmic_GBps": nbytes / ms / 1e6, "frac_of_peak": nbytes / ms / 1e6 / peak}
-    assert rt.device_status() == 0
-    cpu = None if args.no_cpu_baseline else cpu_cluster(n, width, out_width, bits)
-    line = {"metric": "cluster_linear_reconstruct_nodes_per_s", "value": n / (ms_epoch * 1e-3) / 1e6, "unit": "Mnode/s",
-            "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_epoch,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "cluster: Compressgnn_Cluster + Linear 128->256 + Compressgnn_Reconstruct(relu), fwd+bwd",
-                       "nodes": n, "feature_width": width, "out_width": out_width, "bits": bits, "centroids": 4096,
-                       "active_buckets": active, "refresh_interval": 5, "refreshes": cluster.refresh_count,
-                       "l2": "inputs larger than L2 (X is %.0f MB)" % (4e-6 * n * width)},
-            "operators": op_report, "peak_GBps": peak, "clocks": clocks.summary(),
-            "gpu_launches": None}
-    if cpu is not None:
-        line["cpu_baseline"] = cpu
+        op_report[name] = {"ms": ms, "algorithmic_bytes": nbytes, "algorithmic_GBps": nbytes / ms / 1e6,
+                           "frac_of_peak": nbytes / ms / 1e6 / peak}
+    rt.raise_on_device_status()
+    # the operator that moves the most bytes per epoch is the roofline's subject
+    dom = "cluster_reconstruct (bias+relu)"
+    report = {"metric": "cluster_linear_reconstruct_nodes_per_s", "value": n / (ms_epoch * 1e-3) / 1e6, "unit": "Mnode/s",
+              "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms_epoch, "higher_is_better": True,
+              "dtype": "f32", "data": "synthetic",
+              "config": {"workload": "cluster: Compressgnn_Cluster + Linear 128->256 + Compressgnn_Reconstruct(relu), fwd+bwd",
+                         "nodes": n, "feature_width": width, "out_width": out_width, "bits": bits, "centroids": 4096,
+                         "active_buckets": active, "refresh_interval": 5, "refreshes": cluster.refresh_count,
+                         "l2": "inputs larger than L2 (X is %.0f MB)" % (4e-6 * n * width)},
+              "operators": op_report,
+              "roofline": {"bound": "hbm", "kernel": dom, "achieved": op_report[dom]["algorithmic_GBps"], "peak": peak,
+                           "unit": "GB/s", "frac": op_report[dom]["frac_of_peak"], "peak_source": peak_src,
+                           "traffic": None, "traffic_source": "see the ncu summary of the cluster kernels (600 k nodes)",
+                           "algorithmic_bytes_per_launch": op_report[dom]["algorithmic_bytes"],
+                           "ms_per_launch": op_report[dom]["ms"]},
+              "clocks": clocks.summary()}
+    del x, grad_out, y, reps, table, xd
+    if with_cpu:
+        report["cpu_baseline"] = cpu_cluster(n, width, out_width, bits)
+    return report
+
+
+def run_cluster(args):
+    import torch
+    torch.cuda.set_device(0)
+    report = measure_cluster(args.cluster_nodes, args.steps, args.warmup, with_cpu=not args.no_cpu_baseline)
+    line = dict(report, n_gpus=1, scaling="strong", vs_baseline=None, gpu_launches=None)
     print(json.dumps(line))
 
 
-def run_gcn(args):
+def cpu_gcn_epoch(data, width, classes=47, hidden=128, bits=16, epochs=3):
+    """One training epoch of the same 2-layer model on the host cores (all threads): propagation by the
+    reference's CPU spmm_func chain (forward and, through a small autograd wrapper, backward), bucket
+    assignment by its cluster_forward, means / Linear / reconstruct by the torch CPU formulas of its
+    layers (layer/CompressgnnCluster.py:16-25, layer/CompressgnnReconstruct.py:39-42)."""
+    import torch
+    from oracle import oracle
+    rt, _off = oracle.reference_modules()
+    if rt is None:
+        return {"value": None, "unit": "ms", "cores": 0, "kind": "reference",
+                "sample": "unavailable: oracle/_ref is not built on this box"}
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    g = data.edge_index
+    n = g.vertex_cnt
+    fwd = dict(r2v=g.r2v_graph.csr(), v2r=g.v2r_graph.csr(), v2v=g.v2v_graph.csr(), levels=[l.csr() for l in g.r2r_graph])
+    bwd = dict(v2r_t=g.v2r_graph.csc(), v2v_t=g.v2v_graph.csc(), r2v_t=g.r2v_graph.csc(),
+               levels_t=[l.csc() for l in g.r2r_graph])
+    spmm = lambda blk, m, out=None: rt.spmm_func(blk[0], blk[1], blk[2], m, "rowbalance", out)
+
+    class Propagate(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, x):
+            rule = spmm(fwd["r2v"], x)
+            for lvl in fwd["levels"]:
+                rule = spmm(lvl, rule, rule)
+            return spmm(fwd["v2v"], x, spmm(fwd["v2r"], rule))
+
+        @staticmethod
+        def backward(ctx, grad):
+            grad = grad.contiguous()
+            rule = spmm(bwd["v2r_t"], grad)
+            for lvl in reversed(bwd["levels_t"]):
+                rule = spmm(lvl, rule, rule)
+            return spmm(bwd["r2v_t"], rule, spmm(bwd["v2v_t"], grad))
+
+    gen = torch.Generator().manual_seed(5)
+    x = torch.randn(n, width, generator=gen)
+    y = torch.randint(0, classes, (n, 1), generator=gen)
+    lins = [torch.nn.Linear(width, hidden), torch.nn.Linear(hidden, classes)]
+    planes = [torch.randn(width, bits, generator=gen), torch.randn(hidden, bits, generator=gen)]
+    opt = torch.optim.Adam([p for l in lins for p in l.parameters()], lr=1e-3)
+    state = [None, None]
+
+    def layer(i, h, refresh):
+        p = Propagate.apply(h)
+        if refresh or state[i] is None:
+            ids, active = rt.cluster_forward(p.detach().contiguous(), planes[i], bits)
+            index = ids.long()
+            state[i] = (index, torch.bincount(index, minlength=active + 1).clamp_min(1).to(torch.float32))
+        index, counts = state[i]
+        reps = torch.zeros(counts.numel(), p.size(1)).index_add_(0, index, p) / counts[:, None]
+        return torch.nn.functional.linear(reps, lins[i].weight, None).index_select(0, index) + lins[i].bias
+
+    def epoch(e):
+        opt.zero_grad(set_to_none=True)
+        h = torch.nn.functional.dropout(layer(0, x, e % 5 == 0).relu(), 0.3)
+        loss = -torch.log_softmax(layer(1, h, e % 5 == 0), 1).gather(1, y).mean()
+        loss.backward()
+        opt.step()
+
+    epoch(0)
+    t0 = time.perf_counter()
+    for e in range(1, epochs + 1):
+        epoch(e)
+    ms = (time.perf_counter() - t0) / epochs * 1e3
+    return {"value": ms, "unit": "ms", "cores": cores, "kind": "reference", "feature_width": width,
+            "sample": f"whole graph, {epochs} epochs after one warm-up epoch (none of them a refresh epoch)"}
+
+
+def measure_gcn(graph, e_orig, steps, warmup, world, rank, device, widths=(16, 64, 256, 1024)):
     """Config 5: end-to-end 2-layer GCN with propagation and transformation compression
-    (use_transformation=True, H=16, refresh_interval=5) on the config-2 graph, 47 uniform classes,
-    input feature width swept over 16/64/256/1024.  A step = one training epoch (forward, NLL loss
-    on all nodes, backward, Adam step), timed after warm-up epochs as the reference's
+    (use_transformation=True, H=16, refresh_interval=5) on the config-2 graph (already on `device`),
+    47 uniform classes, input feature width swept over 16/64/256/1024.  A step = one training epoch
+    (forward, NLL loss on all nodes, backward, Adam step), timed after warm-up epochs as the reference's
     benchmark/end2end/compressgnn_gcn.py does.  With N GPUs the feature columns of every layer are
     sharded (strong scaling: the same model and matrix on more GPUs) and the graph is replicated."""
     import torch
     import torch.distributed as dist
     from compressgnn_b200.model import GCN
     from compressgnn_b200 import dist as cdist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keep NCCL's banner off stdout (one JSON line)
-        dist.init_process_group("nccl", device_id=device)
-    data, e_orig = build_graph("propagation")
-    graph = data.edge_index
+    from compressgnn_b200 import runtime as rt
     n = graph.vertex_cnt
-    graph.to(device)
     gen = torch.Generator(device=device).manual_seed(5)  # the same labels and features on every rank
     y = torch.randint(0, 47, (n,), device=device, generator=gen)
     y_col = y.unsqueeze(1)
     report = {}
-    for width in (16, 64, 256, 1024):
+    for width in widths:
         x = torch.randn(n, width, device=device, generator=gen)
         torch.manual_seed(5)
         model = GCN(width, 47, hidden_features=128, param_H=16, dropout=0.3, use_transformation=True,
@@ -562,12 +762,10 @@ def run_gcn(args):
             # F.nll_loss, whose CUDA kernels take 0.5 ms per epoch at this size
             loss = -net(x, graph).gather(1, y_col).mean()
             loss.backward()
-            if world > 1:
-                net.sync_gradients()
-            opt.step()
+            opt.step()  # N > 1: every rank steps on the weight rows it owns (see ShardedGCN.consolidate_parameters)
             return loss
 
-        for e in range(max(args.warmup, 3)):
+        for e in range(max(warmup, 3)):
             epoch(e)
         net.reset_cache()
         torch.cuda.synchronize()
@@ -576,63 +774,79 @@ def run_gcn(args):
             torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        for e in range(args.steps):
+        for e in range(steps):
             loss = epoch(e)
         stop.record()
         torch.cuda.synchronize()
-        ms = start.elapsed_time(stop) / args.steps
+        ms = start.elapsed_time(stop) / steps
         if world > 1:
             t = torch.tensor([ms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
+        if world > 1:
+            net.consolidate_parameters()
         report[str(width)] = {"epoch_ms": ms, "final_loss": float(loss.detach())}
         del model, net, opt, x
-    from compressgnn_b200 import runtime as rt
-    assert rt.device_status() == 0
-    if world > 1:
-        dist.destroy_process_group()
-    if rank != 0:
-        return
-    line = {"metric": "gcn_epoch_ms", "value": report["256"]["epoch_ms"], "unit": "ms", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": report["256"]["epoch_ms"],
-            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+    rt.raise_on_device_status()
+    return {"metric": "gcn_epoch_ms", "unit": "ms", "steps": steps, "warmup": max(warmup, 3), "n_gpus": world,
+            "scaling": "strong", "higher_is_better": False, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "gcn: 2-layer GCN, propagation + transformation compression, config-2 graph",
                        "nodes": n, "orig_edges": e_orig, "rules": graph.rule_cnt, "levels": graph.step, "classes": 47,
                        "hidden": 128, "bits": 16, "refresh_interval": 5, "compressor": COMPRESS,
                        "parallelism": f"feature columns of every layer sharded over {world} GPU(s), graph replicated; "
-                                      "collectives: projection all-reduce on refresh epochs, representative "
-                                      "all-gather and gradient all-reduces every epoch"},
-            "epoch_ms_by_feature_width": report, "gpu_launches": None}
+                                      "collectives: projection all-reduce on refresh epochs; per hidden layer and "
+                                      "epoch one all-gather of the representatives and one reduce-scatter of "
+                                      "their gradient; no weight-gradient exchange (each rank steps on the "
+                                      "weight rows it owns)"},
+            "epoch_ms_by_feature_width": report}
+
+
+def run_gcn(args):
+    import torch.distributed as dist
+    world, rank, _local_rank, device = init_ranks()
+    data, e_orig = build_graph("propagation")
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_gcn_epoch(data, 256)
+    graph = data.edge_index
+    graph.to(device)
+    report = measure_gcn(graph, e_orig, args.steps, args.warmup, world, rank, device)
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    ms = report["epoch_ms_by_feature_width"]["256"]["epoch_ms"]
+    line = dict(report, value=ms, ms_per_step=ms, vs_baseline=None, gpu_launches=None)
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
     print(json.dumps(line))
 
 
 def run_reference(args):
-    """The reference's CPU implementation of the same workload, on this box's host cores."""
+    """The reference's CPU implementation of the same workload, on this box's host cores: the same
+    graph, inputs, `config`, steps and warm-up as the GPU arm."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    wl = dict(WORKLOADS[args.workload])
-    if args.width:
-        wl["width"] = args.width
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    width_total, width = widths_for(args, world)
     data, e_orig = build_graph(args.workload)
-    # The CPU has no GPUs to scale over: it runs one 256-column block per step whatever N is; in the
-    # weak-scaling configuration (N blocks) the time per step is N times that, the throughput the same.
-    sec, kind, cores, sample = cpu_propagation(data, wl["width"], args.steps, min(args.warmup, 2))
-    blocks = world if args.scaling == "weak" else 1
+    warmup = max(args.warmup, 3)
+    # The CPU has no GPUs to scale over.  Strong scaling: it runs the whole job (all columns) whatever N
+    # is.  Weak scaling (N blocks of columns): one block is timed and the step time multiplied by N.
+    base = args.width or WORKLOADS[args.workload]["width"]
+    x, grad = host_inputs(data.edge_index.vertex_cnt, base, 1234)
+    sec, kind, cores, sample, _ = cpu_propagation(data, x, grad, args.steps, warmup)
+    blocks = width_total // base
     if blocks > 1:
         sample += f"; one of {blocks} column blocks timed, step time scaled by {blocks}"
-    total_width = wl["width"] * blocks
-    sec *= blocks
-    value = 2 * e_orig * total_width / sec / 1e9
-    g = data.edge_index
+        sec *= blocks
+    value = 2 * e_orig * width_total / sec / 1e9
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
-        "steps": args.steps, "warmup": min(args.warmup, 2), "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: compressed propagation SpMM fwd+bwd, copying-model web graph",
-                   "nodes": g.vertex_cnt, "orig_edges": e_orig, "compressed_edges": g.edge_count(),
-                   "rules": g.rule_cnt, "levels": g.step, "feature_width": total_width, "compressor": COMPRESS},
+        "config": workload_config(args.workload, data, e_orig, width_total, width, world, args.scaling),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -649,13 +863,14 @@ def main():
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cluster", "gcn"], default="propagation")
     ap.add_argument("--cluster-nodes", type=int, default=2450000)
     ap.add_argument("--width", type=int, default=0,
-                    help="feature columns per GPU of a propagation workload (default: the workload's own)")
-    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
-                    help="weak: every GPU holds a full-width (256-column) block of a feature matrix that is "
-                         "N x 256*gpus; strong: the 256 columns are divided among the GPUs")
+                    help="feature columns of a propagation workload (default: the workload's own)")
+    ap.add_argument("--scaling", choices=["strong", "weak"], default="strong",
+                    help="strong: the workload's columns are divided among the GPUs (the same job at every N); "
+                         "weak: every GPU holds a full-width block of a feature matrix that is N x width*gpus")
     ap.add_argument("--cpu-steps", type=int, default=3, help="steps of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the cluster and GCN legs reported under `extra`")
     args = ap.parse_args()
     if args.workload == "cluster":
         run_cluster(args)

@@ -887,6 +887,275 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
     finish_row<T, VW, LPR, VPL>(a, lr.x, lr.w, acc, colbase, colok);
 }
 
+// ---------------------------------------------------------------------------------------
+// Rows of at most a few hundred bytes per column tile: staged through shared memory by 16-byte
+// asynchronous copies (cp.async, one warp-wide instruction per 512 bytes of a gathered row) instead
+// of one bulk copy per row.  The bulk-copy engine of an SM accepts about one copy every ten cycles,
+// which caps 512-byte rows well below what L2 delivers; cp.async goes through the load/store path,
+// needs no registers for the data in flight and no barrier polling: a lane later reads exactly the
+// 16 bytes it copied itself, so `cp.async.wait_group` (the hardware parks the warp) is all the
+// synchronisation there is.  A warp owns a ring of S stages of K gathered rows; the source rows of
+// a 32-entry window sit in registers on the issue side, the values of the window being consumed on
+// the consume side.  Unit decomposition, row order, chunk tickets and summation order are those of
+// seg_kernel, so all engines produce the same bits.  A feature row wider than the tile is covered
+// by blockIdx.y; the tiles of one unit run as separate CTAs, tile 0 of every unit first, which makes
+// the slice of the source matrix that one sweep touches smaller than the whole matrix.
+// ---------------------------------------------------------------------------------------
+#ifndef CGNN_SEG_ASYNC
+#define CGNN_SEG_ASYNC 1
+#endif
+#ifndef CGNN_SEG_ASYNC_K
+#define CGNN_SEG_ASYNC_K 4    // gathered rows per stage
+#endif
+#ifndef CGNN_SEG_ASYNC_S
+#define CGNN_SEG_ASYNC_S 4    // stages per warp
+#endif
+#ifndef CGNN_SEG_ASYNC_RPU
+#define CGNN_SEG_ASYNC_RPU CGNN_SEG_RPU
+#endif
+#ifndef CGNN_SEG_ASYNC_MAX_VECS
+#define CGNN_SEG_ASYNC_MAX_VECS 32   // widest row (in 16-byte vectors) handled as ONE tile by this engine
+#endif
+
+__device__ __forceinline__ void async_copy16(uint32_t dst_shared, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_shared), "l"(src) : "memory");
+}
+__device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// PLAIN: fresh output, no divide, no mask, the width a whole number of tiles -- the propagation
+// passes.  The instantiation drops every per-lane column test and the row epilogue is one store.
+template <typename T, int VW, int VPL, bool PLAIN>
+__global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
+    using V = Vec<T, VW>;
+    static_assert(sizeof(T) * VW == 16, "cp.async staging moves 16-byte vectors");
+    constexpr int LPR = 32, K = CGNN_SEG_ASYNC_K, S = CGNN_SEG_ASYNC_S, RPU = CGNN_SEG_ASYNC_RPU;
+    static_assert(32 % K == 0, "a stage must not straddle two entry windows");
+    constexpr int TILE = 32 * VPL * VW;       // columns of one tile
+    constexpr int SLOT = 32 * VPL * 16;       // bytes of one staged row tile
+    constexpr unsigned FULL = 0xffffffffu;
+    extern __shared__ __align__(128) unsigned char async_smem[];
+    const int lane = threadIdx.x;
+    const uint32_t ring = shared_addr(async_smem) + lane * 16;  // this lane's 16 bytes of slot 0, vector 0
+
+    const int64_t unit = blockIdx.x;
+    const int64_t width = a.width;
+    const int row_bytes = (int)(width * (int64_t)sizeof(T));  // < 2^31: checked by the launcher
+    const int64_t col0 = (int64_t)blockIdx.y * TILE;
+    const int64_t colbase = col0 + lane * VW;
+    bool colok[VPL];
+    V acc[VPL];
+#pragma unroll
+    for (int p = 0; p < VPL; ++p) {
+        colok[p] = PLAIN || colbase + p * (LPR * VW) < width;
+        acc[p] = vec_zero<T, VW>();
+    }
+    const int64_t direct_units = (a.n_direct + RPU - 1) / RPU;
+
+    int e_begin, e_end, nr = 0, myptr = 0;
+    int32_t myrow = 0;
+    int64_t item_index = -1;
+    if (unit < direct_units) {
+        const int64_t first = unit * RPU;
+        nr = (int)min((int64_t)RPU, a.n_direct - first);
+        if (lane <= nr) myptr = a.uptr[first + lane];
+        if (lane < nr) myrow = a.urow ? a.urow[first + lane] : (int32_t)(first + lane);
+        e_begin = __shfl_sync(FULL, myptr, 0);
+        e_end = __shfl_sync(FULL, myptr, nr);
+    } else {
+        item_index = unit - direct_units;
+        if (item_index >= a.n_items) return;  // whole warp
+        const int4 item = a.items[item_index];
+        e_begin = item.y;
+        e_end = item.z;
+    }
+
+    int cur = 0;
+    int row_begin = e_begin;
+    int row_end = item_index >= 0 ? e_end : __shfl_sync(FULL, myptr, 1);
+    char *const obase = reinterpret_cast<char *>(a.out + colbase);  // this lane's first vector of output row 0
+    auto flush = [&]() {  // finish listed row `cur` and move to the next one
+        const int32_t row = __shfl_sync(FULL, myrow, cur);
+        if constexpr (PLAIN) {
+            T *orow = reinterpret_cast<T *>(obase + (int64_t)row * row_bytes);
+#pragma unroll
+            for (int p = 0; p < VPL; ++p) {
+                row_store<T, VW>(orow + p * (LPR * VW), acc[p]);
+                acc[p] = vec_zero<T, VW>();
+            }
+        } else {
+            finish_row<T, VW, LPR, VPL>(a, row, row_begin < row_end ? row_begin : -1, acc, colbase, colok);
+#pragma unroll
+            for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
+        }
+        ++cur;
+        row_begin = row_end;
+        row_end = __shfl_sync(FULL, myptr, (cur + 1) & 31);
+    };
+
+    const int n_ent = e_end - e_begin;
+    const int nb = (n_ent + K - 1) / K;
+    const char *const gbase = reinterpret_cast<const char *>(a.src0 + colbase);  // this lane's first vector of source row 0
+
+    // ---- issue side: source rows of a 32-entry window (lane l holds entry window*32 + l) --------------
+    int32_t o = 0, o_next = 0;
+    if (lane < n_ent) o = entry_row(a, a.entries[e_begin + lane]);
+    if (32 + lane < n_ent) o_next = entry_row(a, a.entries[e_begin + 32 + lane]);
+    int iwindow = 0;
+    auto copy_row = [&](uint32_t slot, int32_t rj) {
+        const char *src = gbase + (int64_t)rj * row_bytes;  // one widening multiply-add
+#pragma unroll
+        for (int p = 0; p < VPL; ++p)
+            if (colok[p]) async_copy16(slot + (uint32_t)(p * 512), src + p * 512);
+    };
+    auto issue = [&](int b) {
+        if (b < nb) {
+            const int first = b * K;
+            if ((first >> 5) != iwindow) {
+                iwindow = first >> 5;
+                o = o_next;
+                const int nxt = (iwindow + 1) * 32 + lane;
+                if (nxt < n_ent) o_next = entry_row(a, a.entries[e_begin + nxt]);
+            }
+            const int cnt = n_ent - first;  // >= 1
+            const uint32_t stage = ring + (uint32_t)((b % S) * K) * SLOT;
+            const int pos = first & 31;
+            if (cnt >= K) {
+#pragma unroll
+                for (int j = 0; j < K; ++j) copy_row(stage + (uint32_t)(j * SLOT), __shfl_sync(FULL, o, pos + j));
+            } else {
+#pragma unroll
+                for (int j = 0; j < K; ++j) {
+                    const int32_t rj = __shfl_sync(FULL, o, pos + j);
+                    if (j < cnt) copy_row(stage + (uint32_t)(j * SLOT), rj);
+                }
+            }
+        }
+        async_commit();  // one group per stage, empty past the end, so that the wait below can count groups
+    };
+#pragma unroll
+    for (int b = 0; b < S; ++b) issue(b);
+
+    // ---- consume side: values of the window being consumed ------------------------------------------
+    T v = T(1), v_next = T(1);
+    if (a.val) {
+        if (lane < n_ent) v = a.val[e_begin + lane];
+        if (32 + lane < n_ent) v_next = a.val[e_begin + 32 + lane];
+    }
+    int cwindow = 0;
+    for (int b = 0; b < nb; ++b) {
+        const int first = b * K;
+        if ((first >> 5) != cwindow) {
+            cwindow = first >> 5;
+            v = v_next;
+            const int nxt = (cwindow + 1) * 32 + lane;
+            if (a.val && nxt < n_ent) v_next = a.val[e_begin + nxt];
+        }
+        async_wait<S - 1>();  // all but the S-1 youngest groups have landed: stage b is in shared memory
+        const int ebase = e_begin + first;
+        const int cnt = n_ent - first;
+        const uint32_t stage = ring + (uint32_t)((b % S) * K) * SLOT;
+        const int pos = first & 31;
+        V x[K][VPL];
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+#pragma unroll
+            for (int p = 0; p < VPL; ++p) {
+                if (colok[p]) {
+                    float4 t;
+                    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(t.x), "=f"(t.y), "=f"(t.z), "=f"(t.w)
+                                 : "r"(stage + (uint32_t)(j * SLOT + p * 512)));
+                    x[j][p] = *reinterpret_cast<V *>(&t);
+                }
+            }
+        }
+        if (cnt >= K && ebase + K <= row_end) {  // a full stage inside the current row
+#pragma unroll
+            for (int j = 0; j < K; ++j) fma_row<T, VW, VPL>(acc, x[j], __shfl_sync(FULL, v, pos + j), colok);
+        } else {
+#pragma unroll
+            for (int j = 0; j < K; ++j) {
+                const T w = __shfl_sync(FULL, v, pos + j);
+                if (j < cnt) {
+                    while (ebase + j >= row_end) flush();
+                    fma_row<T, VW, VPL>(acc, x[j], w, colok);
+                }
+            }
+        }
+        issue(b + S);  // the stage's vectors are in registers: its slots can be refilled
+    }
+    async_wait<0>();
+    if (item_index < 0) {
+        while (cur < nr) flush();
+        return;
+    }
+
+    // ---- chunk of a long row: publish the partial sum, the last ticket adds them up --------
+    const int4 item = a.items[item_index];
+    const int4 lr = a.longs[item.x];
+    T *part = a.partial + item_index * width + colbase;
+#pragma unroll
+    for (int p = 0; p < VPL; ++p)
+        if (colok[p]) vec_store<T, VW>(part + p * (LPR * VW), acc[p]);
+    __threadfence();
+    __syncwarp();
+    int *tk = a.tickets + (int64_t)item.x * gridDim.y + blockIdx.y;
+    int ticket = 0;
+    if (lane == 0) ticket = atomicAdd(tk, 1);
+    ticket = __shfl_sync(FULL, ticket, 0);
+    if (ticket != lr.z - 1) return;
+    __threadfence();
+#pragma unroll
+    for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
+    for (int s = 0; s < lr.z; ++s) {
+        const T *ps = a.partial + (int64_t)(lr.y + s) * width + colbase;
+#pragma unroll
+        for (int p = 0; p < VPL; ++p) {
+            if (colok[p]) {
+                const V q = vec_load_cg<T, VW>(ps + p * (LPR * VW));
+#pragma unroll
+                for (int i = 0; i < VW; ++i) acc[p].v[i] += q.v[i];
+            }
+        }
+    }
+    if (lane == 0) *tk = 0;  // leave the ticket ready for the next launch
+    finish_row<T, VW, LPR, VPL>(a, lr.x, lr.w, acc, colbase, colok);
+}
+
+template <typename T, int VW, int VPL, bool PLAIN>
+static int launch_async_as(const SegArgs<T> &a, cudaStream_t stream) {
+    constexpr size_t BYTES = (size_t)CGNN_SEG_ASYNC_S * CGNN_SEG_ASYNC_K * 32 * VPL * 16;
+    static std::mutex mu;
+    static uint64_t configured = 0;  // one bit per device: the kernel may use BYTES of shared memory
+    int device = 0;
+    CGNN_CUDA(cudaGetDevice(&device));
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (device >= 64 || !(configured >> device & 1)) {
+            CGNN_CUDA(cudaFuncSetAttribute(seg_async_kernel<T, VW, VPL, PLAIN>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BYTES));
+            if (device < 64) configured |= 1ull << device;
+        }
+    }
+    const int64_t gx = ceil_div(a.n_direct, CGNN_SEG_ASYNC_RPU) + a.n_items;
+    const int64_t gy = ceil_div(a.width, (int64_t)32 * VPL * VW);
+    CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
+    seg_async_kernel<T, VW, VPL, PLAIN><<<dim3((unsigned)gx, (unsigned)gy), 32, BYTES, stream>>>(a);
+    CGNN_LAUNCH_CHECK();
+    return CGNN_OK;
+}
+
+template <typename T, int VW, int VPL>
+static int launch_async(const SegArgs<T> &a, cudaStream_t stream) {
+    const bool plain = !a.accumulate && a.div_counts == nullptr && a.seg_mask == nullptr &&
+                       a.width % (32 * VPL * VW) == 0;
+    return plain ? launch_async_as<T, VW, VPL, true>(a, stream) : launch_async_as<T, VW, VPL, false>(a, stream);
+}
+
 template <typename T, int VW, int VPL, bool MASKED>
 static int launch_bulk(const SegArgs<T> &a, cudaStream_t stream) {
     using L = BulkLayout<T, VPL, MASKED>;
@@ -951,6 +1220,14 @@ static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
         }
 #endif
     }
+#if CGNN_SEG_ASYNC
+    if constexpr (sizeof(T) * VW == 16 && !MASKED && !GENERIC) {
+        if (a.seg_mask == nullptr && vecs >= CGNN_SEG_BULK_MIN_VECS && a.width * (int64_t)sizeof(T) < 0x7fffffffll) {
+            if (vecs <= 32 || vecs > CGNN_SEG_ASYNC_MAX_VECS) return launch_async<T, VW, 1>(a, stream);
+            if (vecs <= 64) return launch_async<T, VW, 2>(a, stream);
+        }
+    }
+#endif
 #if CGNN_SEG_BULK
     if constexpr (sizeof(T) * VW == 16) {
         // staged rows: measured faster than register gathers from 17 vectors (272 bytes) up
@@ -969,10 +1246,10 @@ static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
 
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-// Tickets are kept per (long row, column tile).  The staged path in fp64 has the narrowest tiles
-// of a multi-tile launch (128 columns), so this bounds gridDim.y of every configuration
+// Tickets are kept per (long row, column tile).  The cp.async path in fp64 has the narrowest tiles
+// of a multi-tile launch (64 columns), so this bounds gridDim.y of every configuration
 // launch_vw can pick.
-static int64_t ticket_tiles(int64_t width) { return std::max<int64_t>(1, ceil_div(width, 128)); }
+static int64_t ticket_tiles(int64_t width) { return std::max<int64_t>(1, ceil_div(width, 64)); }
 
 // Bytes at the start of a scratch buffer that must be zero before the first launch (and are
 // left zero by every launch): the tickets.

@@ -53,29 +53,35 @@ def gather_columns(local, group=None):
 
 
 class _GatherColumns(torch.autograd.Function):
-    """``[B, F/G]`` column blocks of all ranks -> ``[B, F]`` on every rank.
+    """``[B, F/G]`` column blocks of all ranks -> ``[B, F]`` on every rank: ONE all-gather.
 
     Backward: with ``replicated_consumer`` every rank computes the same thing from the gathered
     matrix, so the incoming gradient is already the full one and the local block is cut out of
-    it; otherwise each rank consumed the matrix for its own slice of the outputs and the
-    gradients are summed over the ranks first.
+    it (no communication); otherwise each rank consumed the matrix for its own slice of the
+    outputs, and ONE reduce-scatter sums the gradients over the ranks and leaves every rank with
+    the block it owns (half the bytes of an all-reduce, and no copy of the full gradient).
     """
 
     @staticmethod
     def forward(ctx, local, group, replicated_consumer):
         ctx.group, ctx.replicated = group, replicated_consumer
         ctx.rank, ctx.world = dist.get_rank(group), dist.get_world_size(group)
-        ctx.width = local.size(-1)
-        return gather_columns(local.contiguous(), group)
+        local = local.contiguous()
+        rows, width = local.shape
+        stacked = torch.empty(ctx.world * rows, width, dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(stacked, local, group=group)   # rank g's block = rows [g*B, (g+1)*B)
+        return stacked.view(ctx.world, rows, width).permute(1, 0, 2).reshape(rows, ctx.world * width)
 
     @staticmethod
     def backward(ctx, grad):
-        grad = grad.contiguous()
-        if not ctx.replicated:
-            grad = grad.clone()
-            dist.all_reduce(grad, op=dist.ReduceOp.SUM, group=ctx.group)
-        begin = ctx.rank * ctx.width
-        return grad[..., begin:begin + ctx.width].contiguous(), None, None
+        rows, width = grad.size(0), grad.size(1) // ctx.world
+        if ctx.replicated:
+            begin = ctx.rank * width
+            return grad[:, begin:begin + width].contiguous(), None, None
+        stacked = grad.view(rows, ctx.world, width).permute(1, 0, 2).contiguous().view(ctx.world * rows, width)
+        mine = torch.empty(rows, width, dtype=grad.dtype, device=grad.device)
+        dist.reduce_scatter_tensor(mine, stacked, op=dist.ReduceOp.SUM, group=ctx.group)
+        return mine, None, None
 
 
 def gather_columns_autograd(local, group=None, replicated_consumer=False):
@@ -169,6 +175,28 @@ class ShardedGCN(torch.nn.Module):
             if i != last and dropout:
                 x = torch.nn.functional.dropout(x, p=self.dropout, training=self.training)
         return torch.nn.functional.log_softmax(x, dim=1)
+
+    def consolidate_parameters(self):
+        """Make every rank's copy of the model whole again after training WITHOUT ``sync_gradients``.
+
+        A hidden layer's weight rows (and bias entries) ``[begin, end)`` are used by one rank only, and
+        that rank sees their full gradient; the other ranks see zeros for them.  With an optimiser that
+        leaves a parameter alone while its gradient is zero (Adam or SGD without weight decay) each
+        rank can therefore step on its own and skip the per-epoch gradient all-reduce; the owners'
+        blocks are gathered here once, when the whole model is needed (evaluation, checkpoint)."""
+        world = dist.get_world_size(self.group)
+        if world == 1:
+            return
+        rank = dist.get_rank(self.group)
+        with torch.no_grad():
+            for layer in self.layers:
+                if not layer.shard_output:
+                    continue  # computed identically on every rank
+                for p in layer.lin.parameters():
+                    begin, end = column_range(p.size(0), rank, world)
+                    whole = torch.empty_like(p)
+                    dist.all_gather_into_tensor(whole, p[begin:end].contiguous(), group=self.group)
+                    p.copy_(whole)
 
     def sync_gradients(self):
         """Sum the hidden layers' parameter gradients over the ranks (one flat all-reduce)."""

@@ -28,7 +28,9 @@ from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 OUT = HERE / "_ref"
-DEFAULT_REFERENCE = Path(os.environ.get("CGNN_REFERENCE_DIR", "/root/reference"))
+# where the reference checkout is looked for: $CGNN_REFERENCE_DIR, else a directory named
+# "reference" beside this repository
+DEFAULT_REFERENCE = Path(os.environ.get("CGNN_REFERENCE_DIR") or HERE.parent.parent / "reference")
 
 
 def _run(cmd):
