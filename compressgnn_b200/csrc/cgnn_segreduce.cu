@@ -913,6 +913,15 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
 #ifndef CGNN_SEG_ASYNC_RPU
 #define CGNN_SEG_ASYNC_RPU CGNN_SEG_RPU
 #endif
+#ifndef CGNN_SEG_ASYNC_EARLY_REFILL
+#define CGNN_SEG_ASYNC_EARLY_REFILL 0  // 1: refill a stage's slots before the arithmetic on its rows
+#endif
+#ifndef CGNN_SEG_ASYNC_ZIGZAG
+#define CGNN_SEG_ASYNC_ZIGZAG 0        // 1: odd column tiles sweep the units in descending order
+#endif
+#ifndef CGNN_SEG_ASYNC_NARROW
+#define CGNN_SEG_ASYNC_NARROW 1        // rows of at most 16 vectors through the cp.async engine as well
+#endif
 #ifndef CGNN_SEG_ASYNC_MAX_VECS
 #define CGNN_SEG_ASYNC_MAX_VECS 32   // widest row (in 16-byte vectors) handled as ONE tile by this engine
 #endif
@@ -928,24 +937,33 @@ __device__ __forceinline__ void async_wait() {
 
 // PLAIN: fresh output, no divide, no mask, the width a whole number of tiles -- the propagation
 // passes.  The instantiation drops every per-lane column test and the row epilogue is one store.
-template <typename T, int VW, int VPL, bool PLAIN>
+// LPR < 32 (rows of at most 256 bytes): a row needs only LPR lanes, so one warp-wide copy brings
+// G = 32 / LPR consecutive entries of the unit's stream, lane group k taking entry k of the step.
+// Every group keeps a partial sum of the current row (its entries in ascending order) and a row is
+// finished by adding the groups' sums with a fixed shuffle tree -- the arrangement of
+// seg_narrow_kernel, fed from shared memory instead of registers.
+template <typename T, int VW, int LPR, int VPL, bool PLAIN>
 __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
     using V = Vec<T, VW>;
     static_assert(sizeof(T) * VW == 16, "cp.async staging moves 16-byte vectors");
-    constexpr int LPR = 32, K = CGNN_SEG_ASYNC_K, S = CGNN_SEG_ASYNC_S, RPU = CGNN_SEG_ASYNC_RPU;
-    static_assert(32 % K == 0, "a stage must not straddle two entry windows");
-    constexpr int TILE = 32 * VPL * VW;       // columns of one tile
-    constexpr int SLOT = 32 * VPL * 16;       // bytes of one staged row tile
+    static_assert(LPR == 32 || VPL == 1, "several vectors per lane only for full-warp rows");
+    constexpr int G = 32 / LPR;               // entries per step (one warp-wide copy per vector)
+    constexpr int K = CGNN_SEG_ASYNC_K, S = CGNN_SEG_ASYNC_S, RPU = LPR == 32 ? CGNN_SEG_ASYNC_RPU : CGNN_SEG_NARROW_RPU;
+    constexpr int KE = K * G;                 // entries per stage
+    static_assert(32 % KE == 0, "a stage must not straddle two entry windows");
+    constexpr int TILE = LPR * VPL * VW;      // columns of one tile
+    constexpr int SLOT = 32 * VPL * 16;       // bytes of one staged step
     constexpr unsigned FULL = 0xffffffffu;
     extern __shared__ __align__(128) unsigned char async_smem[];
     const int lane = threadIdx.x;
+    const int gl = lane & (LPR - 1), gk = lane / LPR;
     const uint32_t ring = shared_addr(async_smem) + lane * 16;  // this lane's 16 bytes of slot 0, vector 0
 
     const int64_t unit = blockIdx.x;
     const int64_t width = a.width;
     const int row_bytes = (int)(width * (int64_t)sizeof(T));  // < 2^31: checked by the launcher
     const int64_t col0 = (int64_t)blockIdx.y * TILE;
-    const int64_t colbase = col0 + lane * VW;
+    const int64_t colbase = col0 + gl * VW;
     bool colok[VPL];
     V acc[VPL];
 #pragma unroll
@@ -973,31 +991,41 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
         e_end = item.z;
     }
 
+    // sum of the groups' partial sums, the same value in every group (fixed tree)
+    auto reduce_groups = [&]() {
+        if constexpr (G > 1) {
+#pragma unroll
+            for (int m = LPR; m < 32; m <<= 1) {
+#pragma unroll
+                for (int i = 0; i < VW; ++i) acc[0].v[i] += __shfl_xor_sync(FULL, acc[0].v[i], m);
+            }
+        }
+    };
     int cur = 0;
     int row_begin = e_begin;
     int row_end = item_index >= 0 ? e_end : __shfl_sync(FULL, myptr, 1);
     char *const obase = reinterpret_cast<char *>(a.out + colbase);  // this lane's first vector of output row 0
     auto flush = [&]() {  // finish listed row `cur` and move to the next one
         const int32_t row = __shfl_sync(FULL, myrow, cur);
-        if constexpr (PLAIN) {
-            T *orow = reinterpret_cast<T *>(obase + (int64_t)row * row_bytes);
+        reduce_groups();
+        if (G == 1 || gk == 0) {
+            if constexpr (PLAIN) {
+                T *orow = reinterpret_cast<T *>(obase + (int64_t)row * row_bytes);
 #pragma unroll
-            for (int p = 0; p < VPL; ++p) {
-                row_store<T, VW>(orow + p * (LPR * VW), acc[p]);
-                acc[p] = vec_zero<T, VW>();
+                for (int p = 0; p < VPL; ++p) row_store<T, VW>(orow + p * (LPR * VW), acc[p]);
+            } else {
+                finish_row<T, VW, LPR, VPL>(a, row, row_begin < row_end ? row_begin : -1, acc, colbase, colok);
             }
-        } else {
-            finish_row<T, VW, LPR, VPL>(a, row, row_begin < row_end ? row_begin : -1, acc, colbase, colok);
-#pragma unroll
-            for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
         }
+#pragma unroll
+        for (int p = 0; p < VPL; ++p) acc[p] = vec_zero<T, VW>();
         ++cur;
         row_begin = row_end;
         row_end = __shfl_sync(FULL, myptr, (cur + 1) & 31);
     };
 
     const int n_ent = e_end - e_begin;
-    const int nb = (n_ent + K - 1) / K;
+    const int nb = (n_ent + KE - 1) / KE;
     const char *const gbase = reinterpret_cast<const char *>(a.src0 + colbase);  // this lane's first vector of source row 0
 
     // ---- issue side: source rows of a 32-entry window (lane l holds entry window*32 + l) --------------
@@ -1013,7 +1041,7 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
     };
     auto issue = [&](int b) {
         if (b < nb) {
-            const int first = b * K;
+            const int first = b * KE;
             if ((first >> 5) != iwindow) {
                 iwindow = first >> 5;
                 o = o_next;
@@ -1022,15 +1050,15 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
             }
             const int cnt = n_ent - first;  // >= 1
             const uint32_t stage = ring + (uint32_t)((b % S) * K) * SLOT;
-            const int pos = first & 31;
-            if (cnt >= K) {
+            const int pos = (first & 31) + gk;
+            if (cnt >= KE) {
 #pragma unroll
-                for (int j = 0; j < K; ++j) copy_row(stage + (uint32_t)(j * SLOT), __shfl_sync(FULL, o, pos + j));
+                for (int j = 0; j < K; ++j) copy_row(stage + (uint32_t)(j * SLOT), __shfl_sync(FULL, o, pos + j * G));
             } else {
 #pragma unroll
                 for (int j = 0; j < K; ++j) {
-                    const int32_t rj = __shfl_sync(FULL, o, pos + j);
-                    if (j < cnt) copy_row(stage + (uint32_t)(j * SLOT), rj);
+                    const int32_t rj = __shfl_sync(FULL, o, (pos + j * G) & 31);
+                    if (j * G + gk < cnt) copy_row(stage + (uint32_t)(j * SLOT), rj);
                 }
             }
         }
@@ -1047,7 +1075,7 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
     }
     int cwindow = 0;
     for (int b = 0; b < nb; ++b) {
-        const int first = b * K;
+        const int first = b * KE;
         if ((first >> 5) != cwindow) {
             cwindow = first >> 5;
             v = v_next;
@@ -1058,7 +1086,7 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
         const int ebase = e_begin + first;
         const int cnt = n_ent - first;
         const uint32_t stage = ring + (uint32_t)((b % S) * K) * SLOT;
-        const int pos = first & 31;
+        const int pos = (first & 31) + gk;
         V x[K][VPL];
 #pragma unroll
         for (int j = 0; j < K; ++j) {
@@ -1073,20 +1101,40 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
                 }
             }
         }
-        if (cnt >= K && ebase + K <= row_end) {  // a full stage inside the current row
+#if CGNN_SEG_ASYNC_EARLY_REFILL
+        issue(b + S);  // the stage's vectors are in registers: its slots can be refilled
+#endif
+        if (cnt >= KE && ebase + KE <= row_end && ebase < row_end) {  // a full stage inside the current row
 #pragma unroll
-            for (int j = 0; j < K; ++j) fma_row<T, VW, VPL>(acc, x[j], __shfl_sync(FULL, v, pos + j), colok);
+            for (int j = 0; j < K; ++j) fma_row<T, VW, VPL>(acc, x[j], __shfl_sync(FULL, v, pos + j * G), colok);
         } else {
+            const int stage_end = ebase + min(cnt, KE);
 #pragma unroll
             for (int j = 0; j < K; ++j) {
-                const T w = __shfl_sync(FULL, v, pos + j);
-                if (j < cnt) {
-                    while (ebase + j >= row_end) flush();
-                    fma_row<T, VW, VPL>(acc, x[j], w, colok);
+                const T w = __shfl_sync(FULL, v, (pos + j * G) & 31);
+                const int s0 = ebase + j * G;           // the step's entries are [s0, s1)
+                const int s1 = min(s0 + G, stage_end);
+                const int mine = s0 + gk;               // this lane group's entry
+                if (s0 < s1) {                          // uniform: the step holds entries of this unit
+                    if (row_end >= s1 && row_end > s0) {  // the current row covers the whole step
+                        if (G == 1 || mine < s1) fma_row<T, VW, VPL>(acc, x[j], w, colok);
+                    } else {                            // one or more rows end inside this step
+                        int lo = s0;
+                        while (true) {
+                            const int hi = min(row_end, s1);
+                            if (mine >= lo && mine < hi) fma_row<T, VW, VPL>(acc, x[j], w, colok);
+                            if (row_end > s1) break;    // the current row goes on in the next step
+                            flush();
+                            lo = hi;
+                            if (cur >= nr) break;
+                        }
+                    }
                 }
             }
         }
-        issue(b + S);  // the stage's vectors are in registers: its slots can be refilled
+#if !CGNN_SEG_ASYNC_EARLY_REFILL
+        issue(b + S);  // the stage's rows are summed: its slots can be refilled
+#endif
     }
     async_wait<0>();
     if (item_index < 0) {
@@ -1095,6 +1143,9 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
     }
 
     // ---- chunk of a long row: publish the partial sum, the last ticket adds them up --------
+    reduce_groups();
+    if (G > 1 && gk != 0) return;
+    const unsigned gmask = LPR == 32 ? FULL : (1u << LPR) - 1u;
     const int4 item = a.items[item_index];
     const int4 lr = a.longs[item.x];
     T *part = a.partial + item_index * width + colbase;
@@ -1102,11 +1153,11 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
     for (int p = 0; p < VPL; ++p)
         if (colok[p]) vec_store<T, VW>(part + p * (LPR * VW), acc[p]);
     __threadfence();
-    __syncwarp();
+    __syncwarp(gmask);
     int *tk = a.tickets + (int64_t)item.x * gridDim.y + blockIdx.y;
     int ticket = 0;
     if (lane == 0) ticket = atomicAdd(tk, 1);
-    ticket = __shfl_sync(FULL, ticket, 0);
+    ticket = __shfl_sync(gmask, ticket, 0);
     if (ticket != lr.z - 1) return;
     __threadfence();
 #pragma unroll
@@ -1126,9 +1177,10 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
     finish_row<T, VW, LPR, VPL>(a, lr.x, lr.w, acc, colbase, colok);
 }
 
-template <typename T, int VW, int VPL, bool PLAIN>
+template <typename T, int VW, int LPR, int VPL, bool PLAIN>
 static int launch_async_as(const SegArgs<T> &a, cudaStream_t stream) {
     constexpr size_t BYTES = (size_t)CGNN_SEG_ASYNC_S * CGNN_SEG_ASYNC_K * 32 * VPL * 16;
+    constexpr int RPU = LPR == 32 ? CGNN_SEG_ASYNC_RPU : CGNN_SEG_NARROW_RPU;
     static std::mutex mu;
     static uint64_t configured = 0;  // one bit per device: the kernel may use BYTES of shared memory
     int device = 0;
@@ -1136,24 +1188,25 @@ static int launch_async_as(const SegArgs<T> &a, cudaStream_t stream) {
     {
         std::lock_guard<std::mutex> lock(mu);
         if (device >= 64 || !(configured >> device & 1)) {
-            CGNN_CUDA(cudaFuncSetAttribute(seg_async_kernel<T, VW, VPL, PLAIN>,
+            CGNN_CUDA(cudaFuncSetAttribute(seg_async_kernel<T, VW, LPR, VPL, PLAIN>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, (int)BYTES));
             if (device < 64) configured |= 1ull << device;
         }
     }
-    const int64_t gx = ceil_div(a.n_direct, CGNN_SEG_ASYNC_RPU) + a.n_items;
-    const int64_t gy = ceil_div(a.width, (int64_t)32 * VPL * VW);
+    const int64_t gx = ceil_div(a.n_direct, RPU) + a.n_items;
+    const int64_t gy = ceil_div(a.width, (int64_t)LPR * VPL * VW);
     CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
-    seg_async_kernel<T, VW, VPL, PLAIN><<<dim3((unsigned)gx, (unsigned)gy), 32, BYTES, stream>>>(a);
+    seg_async_kernel<T, VW, LPR, VPL, PLAIN><<<dim3((unsigned)gx, (unsigned)gy), 32, BYTES, stream>>>(a);
     CGNN_LAUNCH_CHECK();
     return CGNN_OK;
 }
 
-template <typename T, int VW, int VPL>
+template <typename T, int VW, int LPR, int VPL>
 static int launch_async(const SegArgs<T> &a, cudaStream_t stream) {
     const bool plain = !a.accumulate && a.div_counts == nullptr && a.seg_mask == nullptr &&
-                       a.width % (32 * VPL * VW) == 0;
-    return plain ? launch_async_as<T, VW, VPL, true>(a, stream) : launch_async_as<T, VW, VPL, false>(a, stream);
+                       a.width % (LPR * VPL * VW) == 0;
+    return plain ? launch_async_as<T, VW, LPR, VPL, true>(a, stream)
+                 : launch_async_as<T, VW, LPR, VPL, false>(a, stream);
 }
 
 template <typename T, int VW, int VPL, bool MASKED>
@@ -1207,6 +1260,21 @@ static int launch_cfg(const SegArgs<T> &a, cudaStream_t stream) {
 template <typename T, int VW, bool MASKED, bool GENERIC>
 static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
     const int64_t vecs = a.width / VW;
+#if CGNN_SEG_ASYNC
+    if constexpr (sizeof(T) * VW == 16 && !MASKED && !GENERIC) {
+        if (a.seg_mask == nullptr && a.width * (int64_t)sizeof(T) < 0x7fffffffll) {
+#if CGNN_SEG_ASYNC_NARROW
+            if (vecs <= 4) return launch_async<T, VW, 4, 1>(a, stream);
+            if (vecs <= 8) return launch_async<T, VW, 8, 1>(a, stream);
+            if (vecs <= 16) return launch_async<T, VW, 16, 1>(a, stream);
+#endif
+            if (vecs >= CGNN_SEG_BULK_MIN_VECS) {
+                if (vecs <= 32 || vecs > CGNN_SEG_ASYNC_MAX_VECS) return launch_async<T, VW, 32, 1>(a, stream);
+                if (vecs <= 64) return launch_async<T, VW, 32, 2>(a, stream);
+            }
+        }
+    }
+#endif
     if constexpr (!MASKED && !GENERIC) {
 #if CGNN_SEG_NARROW
         // measured on B200 (325 k-node graph, fused vertex pass, single-warp CTAs): side-by-side
@@ -1220,14 +1288,6 @@ static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
         }
 #endif
     }
-#if CGNN_SEG_ASYNC
-    if constexpr (sizeof(T) * VW == 16 && !MASKED && !GENERIC) {
-        if (a.seg_mask == nullptr && vecs >= CGNN_SEG_BULK_MIN_VECS && a.width * (int64_t)sizeof(T) < 0x7fffffffll) {
-            if (vecs <= 32 || vecs > CGNN_SEG_ASYNC_MAX_VECS) return launch_async<T, VW, 1>(a, stream);
-            if (vecs <= 64) return launch_async<T, VW, 2>(a, stream);
-        }
-    }
-#endif
 #if CGNN_SEG_BULK
     if constexpr (sizeof(T) * VW == 16) {
         // staged rows: measured faster than register gathers from 17 vectors (272 bytes) up
