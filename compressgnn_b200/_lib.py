@@ -26,6 +26,7 @@ SIGNATURES = {
     "cgnn_plan_destroy": (None, [_c_ptr]),
     "cgnn_plan_info": (_c_int, [_c_ptr, ctypes.POINTER(_c_i64)]),
     "cgnn_plan_source_rows": (_c_int, [_c_ptr, ctypes.POINTER(_c_i64)]),
+    "cgnn_plan_degrees": (_c_int, [_c_ptr, ctypes.POINTER(_c_i64)]),
     "cgnn_plan_scratch_bytes": (_c_size, [_c_ptr, _c_i64, _c_int]),
     "cgnn_plan_ticket_bytes": (_c_size, [_c_ptr, _c_i64, _c_int]),
     "cgnn_spmm": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr,

@@ -395,7 +395,24 @@ struct HostSegments {
     std::mutex lock;
     const void *workspace = nullptr;
     int64_t n = 0, valid = 0;
-    std::vector<int32_t> start;
+    int32_t *start = nullptr;          // page-locked, grow-only (the copy into it must not be staged)
+    size_t capacity = 0;               // in words
+    std::vector<int32_t> pageable;     // used when page-locked memory cannot be had
+    int32_t *reserve(size_t words) {
+        if (capacity < words) {
+            if (start && start != pageable.data()) cudaFreeHost(start);
+            void *p = nullptr;
+            if (cudaHostAlloc(&p, sizeof(int32_t) * words, cudaHostAllocDefault) == cudaSuccess) {
+                start = static_cast<int32_t *>(p);
+            } else {
+                cudaGetLastError();
+                pageable.resize(words);
+                start = pageable.data();
+            }
+            capacity = words;
+        }
+        return start;
+    }
 };
 static HostSegments &host_segments() {
     static HostSegments hs;
@@ -502,12 +519,12 @@ int cgnn_cluster_assign(const int32_t *codes, int64_t n, int bits, void *workspa
     const int64_t want = std::min<int64_t>(n + 2, std::min<int64_t>(((int64_t)1 << bits) + 2, (int64_t)1 << 20));
     hs.workspace = workspace;
     hs.n = n;
-    hs.start.resize((size_t)want);
-    int32_t active = 0;
-    CGNN_CUDA(cudaMemcpyAsync(&active, L.active, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
-    CGNN_CUDA(cudaMemcpyAsync(hs.start.data(), L.segstart, sizeof(int32_t) * (size_t)want,
+    int32_t *host = hs.reserve((size_t)want + 1);  // [0] receives `active`, the segment starts follow
+    CGNN_CUDA(cudaMemcpyAsync(host, L.active, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    CGNN_CUDA(cudaMemcpyAsync(host + 1, L.segstart, sizeof(int32_t) * (size_t)want,
                               cudaMemcpyDeviceToHost, stream));
     CGNN_CUDA(cudaStreamSynchronize(stream));
+    const int32_t active = host[0];
     hs.valid = (int64_t)active + 2 <= want ? (int64_t)active + 2 : 0;
     *active_out = active;
     return CGNN_OK;
@@ -540,7 +557,7 @@ int cgnn_cluster_assign_export(const void *workspace, int64_t n, int64_t active,
         HostSegments &hs = host_segments();
         std::lock_guard<std::mutex> guard(hs.lock);
         const bool have = hs.workspace == workspace && hs.n == n && hs.valid == active + 2;
-        rc = plan_build(p, rp, cl, split, stream, have ? hs.start.data() : nullptr, false);
+        rc = plan_build(p, rp, cl, split, stream, have ? hs.start + 1 : nullptr, false);
     }
     if (rc != CGNN_OK) {
         cgnn_plan_destroy(p);

@@ -97,6 +97,21 @@ __device__ __forceinline__ void vec_store_cs(T *p, const Vec<T, VW> &x) {
     }
 }
 
+// Page-locked host scratch of the calling thread, grow-only, reused from call to call (the callers
+// synchronise their stream before they return).  Copies to and from pageable memory are staged by
+// the driver and cost the host ~100 us each; an assignment refresh makes four of them.  Returns
+// nullptr when page-locked memory cannot be had or `bytes` exceeds the cap: use pageable memory then.
+void *pinned_scratch(size_t bytes, int slot);
+// Marks the slot as read by work queued on `stream` up to now: the next pinned_scratch() of the slot
+// waits for that work (normally long finished) instead of the caller synchronising the stream.
+void pinned_scratch_in_use(int slot, cudaStream_t stream);
+
+// Stream-ordered device allocation from a pool the library owns (one per device, nothing is given
+// back to the driver until the process ends): a plan is built and dropped at every assignment
+// refresh, and with the default pool's release threshold of zero every cudaMallocAsync after a
+// synchronisation went back to the driver (~250 us of host time).
+cudaError_t pool_alloc(void **ptr, size_t bytes, cudaStream_t stream);
+
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 static inline size_t align_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
 

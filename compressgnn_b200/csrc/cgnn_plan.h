@@ -28,6 +28,7 @@ struct cgnn_plan {
     int4 *items = nullptr;         // device {long row index, first entry, end entry, 0}
     int4 *longs = nullptr;         // device {row, first item, items, first entry of the row}
     int compact = 0;               // 1: empty rows are not listed (a fresh output is cleared first)
+    int64_t degree_p50 = 0, degree_p99 = 0, degree_max = 0;  // row-length histogram the split was chosen from
     int64_t source_rows[2] = {0, 0};  // 1 + the largest source row each term refers to (0: no entries)
     void *block = nullptr;         // the one device allocation all arrays above live in
     cudaStream_t home = nullptr;   // stream the block was allocated on (stream-ordered allocator)

@@ -1,19 +1,24 @@
 // Segment reduce: out[r,:] (+)= sum over the entries of row r of  val[e] * src[col[e],:].
 //
-// One kernel serves the compressed-propagation SpMM blocks, the fused two-block pass, the
+// One decomposition serves the compressed-propagation SpMM blocks, the fused two-block pass, the
 // per-bucket mean and the reconstruct backward.  Design points (B200, HBM-bound):
-//   * the plan stores the entries of the short rows back to back, so a group of LPR lanes
-//     that owns a few consecutive rows reads ONE contiguous entry range: LPR (source,value)
-//     pairs per coalesced load (the next batch is requested before the current one is
-//     consumed), broadcast by shuffle; U gathered feature rows are in flight per lane before
-//     the FMAs issue, across row boundaries, so a short row costs no pipeline restart;
-//   * every lane keeps VPL 16-byte vectors of the current row in registers, so one gathered
-//     feature row is LPR*VPL coalesced 128-bit loads;
-//   * rows longer than `split` are cut into chunks (work units of their own); a chunk
-//     writes its partial sum to scratch, takes a ticket, and the chunk that draws the last
-//     ticket adds the partials in chunk order -- deterministic, no float atomics, and no
-//     unit ever waits for another.
+//   * the plan stores the entries of the short rows back to back, so a work unit that owns a few
+//     consecutive rows reads ONE contiguous entry range, 32 (source,value) pairs per coalesced
+//     load, the next window requested before the current one is consumed;
+//   * rows longer than `split` are cut into chunks (work units of their own); a chunk writes its
+//     partial sum to scratch, takes a ticket, and the chunk that draws the last ticket adds the
+//     partials in chunk order -- deterministic, no float atomics, and no unit ever waits for another;
+//   * three gather engines share that decomposition and produce the same bits:
+//       seg_async_kernel  gathered rows staged through shared memory by 16-byte cp.async copies, one
+//                         warp-wide instruction per 512 bytes; rows narrower than 512 bytes bring
+//                         several entries per instruction.  The engine of every plain launch on
+//                         16-byte aligned rows (column tiles of 128 fp32 columns).
+//       seg_bulk_kernel   rows staged by one bulk copy (cp.async.bulk + mbarrier) per row; kept for
+//                         the launches that also stage a mask row per entry or per output row.
+//       seg_kernel        register gathers; scalar rows, unaligned operands, two source matrices
+//                         that are not a whole number of rows apart.
 #include <algorithm>
+#include <cmath>
 #include <cstring>
 #include <mutex>
 #include <vector>
@@ -30,9 +35,6 @@
 #ifndef CGNN_SEG_RPU
 #define CGNN_SEG_RPU 8      // rows per direct work unit (capped by the lane-group width)
 #endif
-#ifndef CGNN_SEG_NARROW
-#define CGNN_SEG_NARROW 1   // side-by-side lane groups for rows of at most 16 vectors
-#endif
 #ifndef CGNN_SEG_PREFETCH
 #define CGNN_SEG_PREFETCH 1    // request the next (source,value) batch before consuming the current
 #endif
@@ -44,16 +46,6 @@
 #endif
 #ifndef CGNN_SEG_THREADS
 #define CGNN_SEG_THREADS 128
-#endif
-#ifndef CGNN_SEG_OUT_HINT
-#define CGNN_SEG_OUT_HINT 0   // finished rows: 0 plain store, 1 streaming store (st.cs), 2 L2 evict-first policy
-#endif
-#ifndef CGNN_SEG_LOAD_HINT
-#define CGNN_SEG_LOAD_HINT 0  // staged rows: 0 no hint, 1 all evict-last, 2 near evict-last / far evict-first,
-                              // 3 near evict-last / far no hint, 4 all evict-first
-#endif
-#ifndef CGNN_SEG_NEAR_WINDOW
-#define CGNN_SEG_NEAR_WINDOW 4096
 #endif
 #ifndef CGNN_SEG_MINBLOCKS
 #define CGNN_SEG_MINBLOCKS 6
@@ -91,25 +83,12 @@ __device__ __forceinline__ Vec<T, VW> gather_load(const T *p) {
 #endif
 }
 
-// Store of a finished output row (written once, never read again by the launch).
+// Store of a finished output row.  (Streaming and L2 evict-first variants of this store, alone and
+// together with evict-last / evict-first hints on the gathers, changed neither the time nor the DRAM
+// traffic of the vertex pass on B200; a plain store it stays.)
 template <typename T, int VW>
 __device__ __forceinline__ void row_store(T *p, const Vec<T, VW> &x) {
-#if CGNN_SEG_OUT_HINT == 1
-    vec_store_cs<T, VW>(p, x);
-#elif CGNN_SEG_OUT_HINT == 2
-    if constexpr (sizeof(T) * VW == 16) {
-        uint64_t pol;
-        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
-        const float4 t = *reinterpret_cast<const float4 *>(&x);
-        asm volatile("st.global.L2::cache_hint.v4.f32 [%0], {%1, %2, %3, %4}, %5;" ::"l"(p), "f"(t.x), "f"(t.y), "f"(t.z),
-                     "f"(t.w), "l"(pol)
-                     : "memory");
-    } else {
-        vec_store_cs<T, VW>(p, x);
-    }
-#else
     vec_store<T, VW>(p, x);
-#endif
 }
 
 int segreduce_status(int *out) {
@@ -392,184 +371,30 @@ __global__ void __launch_bounds__(CGNN_SEG_THREADS, CGNN_SEG_MINBLOCKS) seg_kern
     finish_row<T, VW, LPR, VPL>(a, lr.x, lr.w, acc, colbase, colok);
 }
 
-// ---------------------------------------------------------------------------------------
-// Narrow rows (at most 16 vectors wide, i.e. F <= 64 in fp32): a feature row needs only LPR < 32
-// lanes, so a warp works on ONE work unit with its 32/LPR lane groups side by side -- group k
-// takes entries k, k+G, k+2G, ... of the unit's stream.  All groups follow the same loop (no
-// divergence between them, one coalesced entry load per 32 entries for the whole warp); each
-// keeps a partial sum of the current row, and a row is finished by adding the groups' partial
-// sums with a fixed shuffle tree.
-// ---------------------------------------------------------------------------------------
+// Rows of at most 16 vectors (F <= 64 in fp32) go through the cp.async engine below with several
+// entries per warp-wide copy; a direct work unit of such rows holds this many of them.
 #ifndef CGNN_SEG_NARROW_RPU
 #define CGNN_SEG_NARROW_RPU 16
 #endif
-#ifndef CGNN_SEG_NARROW_THREADS
-#define CGNN_SEG_NARROW_THREADS 32  // one warp per CTA: a finished unit frees its slot at once (68 -> 58 us at F=16)
-#endif
-
-template <typename T, int VW, int LPR>
-__global__ void __launch_bounds__(CGNN_SEG_NARROW_THREADS) seg_narrow_kernel(const SegArgs<T> a) {
-    using V = Vec<T, VW>;
-    constexpr int G = 32 / LPR;
-    constexpr int U = 8;  // steps (G entries each) in flight per lane
-    constexpr int RPU = CGNN_SEG_NARROW_RPU;
-    constexpr unsigned FULL = 0xffffffffu;
-    const int lane = threadIdx.x & 31;
-    const int gl = lane & (LPR - 1);
-    const int gk = lane / LPR;
-    const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int64_t width = a.width;
-    const int64_t colbase = (int64_t)blockIdx.y * (LPR * VW) + gl * VW;
-    bool colok[1] = {colbase < width};
-    V acc[1] = {vec_zero<T, VW>()};
-    const int64_t direct_units = (a.n_direct + RPU - 1) / RPU;
-
-    int e_begin, e_end, nr = 0, myptr = 0;
-    int32_t myrow = 0;
-    int64_t item_index = -1;
-    if (unit < direct_units) {
-        const int64_t first = unit * RPU;
-        nr = (int)min((int64_t)RPU, a.n_direct - first);
-        if (lane <= nr) myptr = a.uptr[first + lane];
-        if (lane < nr) myrow = a.urow ? a.urow[first + lane] : (int32_t)(first + lane);
-        e_begin = __shfl_sync(FULL, myptr, 0);
-        e_end = __shfl_sync(FULL, myptr, nr);
-    } else {
-        item_index = unit - direct_units;
-        if (item_index >= a.n_items) return;  // whole warp
-        const int4 item = a.items[item_index];
-        e_begin = item.y;
-        e_end = item.z;
-    }
-    int cur = 0;
-    int row_begin = e_begin;
-    int row_end = item_index >= 0 ? e_end : __shfl_sync(FULL, myptr, 1);
-
-    // sum of the groups' partial sums, same value in every group (fixed tree)
-    auto reduce_groups = [&]() {
-        V t = acc[0];
-#pragma unroll
-        for (int m = LPR; m < 32; m <<= 1) {
-#pragma unroll
-            for (int i = 0; i < VW; ++i) t.v[i] += __shfl_xor_sync(FULL, t.v[i], m);
-        }
-        return t;
-    };
-    auto flush = [&]() {  // finish listed row `cur` and move to the next one
-        V t[1] = {reduce_groups()};
-        const int32_t row = __shfl_sync(FULL, myrow, cur);
-        if (gk == 0) finish_row<T, VW, LPR, 1>(a, row, row_begin < row_end ? row_begin : -1, t, colbase, colok);
-        acc[0] = vec_zero<T, VW>();
-        ++cur;
-        row_begin = row_end;
-        row_end = __shfl_sync(FULL, myptr, (cur + 1) & 31);
-    };
-
-    int32_t o = 0, o_next = 0;
-    T v = T(0), v_next = T(0);
-    if (e_begin + lane < e_end) {
-        o = entry_row(a, a.entries[e_begin + lane]);
-        v = a.val ? a.val[e_begin + lane] : T(1);
-    }
-    for (int base = e_begin; base < e_end; base += 32) {
-        const int nxt = base + 32 + lane;
-        if (nxt < e_end) {
-            o_next = entry_row(a, a.entries[nxt]);
-            v_next = a.val ? a.val[nxt] : T(1);
-        }
-        const int cnt = min(32, e_end - base);
-        const int steps = (cnt + G - 1) / G;
-        for (int s0 = 0; s0 < steps; s0 += U) {
-            V x[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int j = (s0 + u) * G + gk;
-                const int32_t oj = __shfl_sync(FULL, o, j & 31);
-                if (j < cnt && colok[0]) x[u] = gather_load<T, VW>(a.src0 + (int64_t)oj * width + colbase);
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int s = s0 + u;
-                const int j = s * G + gk;
-                const T w = __shfl_sync(FULL, v, j & 31);
-                if (s < steps) {  // uniform
-                    const int step_first = base + s * G;
-                    const int step_last = min(step_first + G, base + cnt);
-                    const int e = base + j;
-                    if (step_last <= row_end) {  // the whole step belongs to the current row
-                        if (j < cnt && colok[0]) {
-#pragma unroll
-                            for (int i = 0; i < VW; ++i) acc[0].v[i] = fma(x[u].v[i], w, acc[0].v[i]);
-                        }
-                    } else {  // one or more rows end inside this step
-                        int lo = step_first;
-                        while (true) {
-                            const int hi = min(row_end, step_last);
-                            if (e >= lo && e < hi && colok[0]) {
-#pragma unroll
-                                for (int i = 0; i < VW; ++i) acc[0].v[i] = fma(x[u].v[i], w, acc[0].v[i]);
-                            }
-                            if (row_end > step_last) break;  // the current row goes on in the next step
-                            flush();
-                            lo = hi;
-                            if (cur >= nr) break;
-                        }
-                    }
-                }
-            }
-        }
-        o = o_next;
-        v = v_next;
-    }
-    if (item_index < 0) {
-        while (cur < nr) flush();
-        return;
-    }
-
-    // ---- chunk of a long row: group 0 publishes the partial sum and draws the ticket -------
-    V total[1] = {reduce_groups()};
-    if (gk != 0) return;
-    const unsigned gmask = (1u << LPR) - 1u;
-    const int4 item = a.items[item_index];
-    const int4 lr = a.longs[item.x];
-    T *part = a.partial + item_index * width + colbase;
-    if (colok[0]) vec_store<T, VW>(part, total[0]);
-    __threadfence();
-    __syncwarp(gmask);
-    int *tk = a.tickets + (int64_t)item.x * gridDim.y + blockIdx.y;
-    int ticket = 0;
-    if (gl == 0) ticket = atomicAdd(tk, 1);
-    ticket = __shfl_sync(gmask, ticket, 0, LPR);
-    if (ticket != lr.z - 1) return;
-    __threadfence();
-    total[0] = vec_zero<T, VW>();
-    for (int s = 0; s < lr.z; ++s) {
-        if (colok[0]) {
-            const V q = vec_load_cg<T, VW>(a.partial + (int64_t)(lr.y + s) * width + colbase);
-#pragma unroll
-            for (int i = 0; i < VW; ++i) total[0].v[i] += q.v[i];
-        }
-    }
-    if (gl == 0) *tk = 0;
-    finish_row<T, VW, LPR, 1>(a, lr.x, lr.w, total, colbase, colok);
-}
 
 // ---------------------------------------------------------------------------------------
-// Wide rows (more than 16 vectors, i.e. at least 272 bytes of a row per column tile): the gathered
-// rows are staged through shared memory by bulk asynchronous copies (cp.async.bulk, completion
-// counted on an mbarrier) instead of being loaded into registers.  A warp owns a ring of
-// S stages x B rows; the lane that holds an entry of the unit's stream issues the copy of its
-// source row (so the address of an entry, including the choice between the two source matrices,
-// is computed once by one lane); when a stage's barrier completes the warp moves the stage to
-// registers, refills it at once and then adds the rows to its row sums.  Copies stay in flight
-// while rows are finished and written, and what is in flight per SM is bounded by shared memory,
-// not registers.  Measured on B200: CTAs of ONE warp with an 8 KB ring (about 24 per SM) beat
-// larger CTAs with deeper rings by 20 % -- units differ in length, and a CTA's shared memory is
-// idle from the moment its first warp finishes until its last one does.  Unit decomposition, row
-// order, chunk tickets and summation order are those of seg_kernel, so both kernels produce the
-// same bits.  MASKED: every entry also brings the tile of its mask row (same row index in
-// mask_src) into the second half of the stage, and values whose mask is <= 0 are dropped as the
-// stage moves to registers.
+// Rows staged by bulk copies (at least 272 bytes of a row per column tile): the gathered rows are
+// brought into shared memory by bulk asynchronous copies (cp.async.bulk, completion counted on an
+// mbarrier).  A warp owns a ring of S stages x B rows; the lane that holds an entry of the unit's
+// stream issues the copy of its source row (so the address of an entry, including the choice between
+// the two source matrices, is computed once by one lane); when a stage's barrier completes the warp
+// moves the stage to registers, refills it at once and then adds the rows to its row sums.  CTAs are
+// ONE warp with an 8 KB ring (about 24 per SM): units differ in length, and a CTA's shared memory is
+// idle from the moment its first warp finishes until its last one does.  MASKED: every entry also
+// brings the tile of its mask row (same row index in mask_src) into the second half of the stage, and
+// values whose mask is <= 0 are dropped as the stage moves to registers.
+//
+// What bounds this engine on B200: an SM's bulk-copy unit accepts about one copy per ten cycles (27 G
+// copies/s on the whole GPU), each lane's copy is issued as an instruction of its own, and the
+// barrier is polled.  For 1 KB rows that is enough to saturate DRAM (the masked reconstruct backward
+// runs at the copy bandwidth); for 512-byte rows and less the cp.async engine below is faster
+// (154 -> 113 us on the 128-column vertex pass of the 325 k-node graph), and it took over every plain
+// launch.
 // ---------------------------------------------------------------------------------------
 #ifndef CGNN_SEG_BULK
 #define CGNN_SEG_BULK 1
@@ -623,15 +448,6 @@ __device__ __forceinline__ void bulk_copy_to_shared(void *dst, const void *src, 
                      shared_addr(dst)),
                  "l"(src), "r"(bytes), "r"(shared_addr(bar))
                  : "memory");
-}
-
-__device__ __forceinline__ void bulk_copy_to_shared_hint(void *dst, const void *src, uint32_t bytes, uint64_t *bar,
-                                                         uint64_t policy) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
-            shared_addr(dst)),
-        "l"(src), "r"(bytes), "r"(shared_addr(bar)), "l"(policy)
-        : "memory");
 }
 
 template <typename T, int VPL, bool MASKED>
@@ -724,12 +540,6 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
         o_next = a.entries[e_begin + 32 + lane];
         if (a.val) v_next = a.val[e_begin + 32 + lane];
     }
-#if CGNN_SEG_LOAD_HINT
-    uint64_t pol_last, pol_first;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol_last));
-    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol_first));
-    const int32_t unit_row = item_index >= 0 ? (int32_t)-0x40000000 : __shfl_sync(FULL, myrow, 0);
-#endif
     int window = 0;
     auto issue = [&](int b) {
         const int first = b * B;  // position of the stage's first entry in the unit's stream
@@ -751,30 +561,8 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
         if (j >= 0 && j < cnt) {
             const int64_t off = (int64_t)(o & 0x7fffffff) * width + col0;
             meta[st * B + j] = v;
-#if CGNN_SEG_LOAD_HINT == 1
-            bulk_copy_to_shared_hint(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off, slot_bytes,
-                                     &bars[st], pol_last);
-#elif CGNN_SEG_LOAD_HINT == 4
-            bulk_copy_to_shared_hint(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off, slot_bytes,
-                                     &bars[st], pol_first);
-#elif CGNN_SEG_LOAD_HINT == 2 || CGNN_SEG_LOAD_HINT == 3
-            {
-                const int32_t dist = (o & 0x7fffffff) - unit_row;
-                const bool near = o >= 0 || (dist >= -CGNN_SEG_NEAR_WINDOW && dist <= CGNN_SEG_NEAR_WINDOW);
-                if (near)
-                    bulk_copy_to_shared_hint(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off,
-                                             slot_bytes, &bars[st], pol_last);
-                else if (CGNN_SEG_LOAD_HINT == 2)
-                    bulk_copy_to_shared_hint(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off,
-                                             slot_bytes, &bars[st], pol_first);
-                else
-                    bulk_copy_to_shared(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off,
-                                        slot_bytes, &bars[st]);
-            }
-#else
             bulk_copy_to_shared(ring + (size_t)(st * PARTS * B + j) * SLOT, (o < 0 ? src1 : a.src0) + off, slot_bytes,
                                 &bars[st]);
-#endif
             if constexpr (MASKED)
                 bulk_copy_to_shared(ring + (size_t)(st * PARTS * B + B + j) * SLOT, a.mask_src + off, slot_bytes,
                                     &bars[st]);
@@ -912,15 +700,6 @@ __global__ void __launch_bounds__(CGNN_SEG_BULK_WARPS * 32) seg_bulk_kernel(cons
 #endif
 #ifndef CGNN_SEG_ASYNC_RPU
 #define CGNN_SEG_ASYNC_RPU CGNN_SEG_RPU
-#endif
-#ifndef CGNN_SEG_ASYNC_EARLY_REFILL
-#define CGNN_SEG_ASYNC_EARLY_REFILL 0  // 1: refill a stage's slots before the arithmetic on its rows
-#endif
-#ifndef CGNN_SEG_ASYNC_ZIGZAG
-#define CGNN_SEG_ASYNC_ZIGZAG 0        // 1: odd column tiles sweep the units in descending order
-#endif
-#ifndef CGNN_SEG_ASYNC_NARROW
-#define CGNN_SEG_ASYNC_NARROW 1        // rows of at most 16 vectors through the cp.async engine as well
 #endif
 #ifndef CGNN_SEG_ASYNC_MAX_VECS
 #define CGNN_SEG_ASYNC_MAX_VECS 32   // widest row (in 16-byte vectors) handled as ONE tile by this engine
@@ -1101,9 +880,6 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
                 }
             }
         }
-#if CGNN_SEG_ASYNC_EARLY_REFILL
-        issue(b + S);  // the stage's vectors are in registers: its slots can be refilled
-#endif
         if (cnt >= KE && ebase + KE <= row_end && ebase < row_end) {  // a full stage inside the current row
 #pragma unroll
             for (int j = 0; j < K; ++j) fma_row<T, VW, VPL>(acc, x[j], __shfl_sync(FULL, v, pos + j * G), colok);
@@ -1132,9 +908,7 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
                 }
             }
         }
-#if !CGNN_SEG_ASYNC_EARLY_REFILL
         issue(b + S);  // the stage's rows are summed: its slots can be refilled
-#endif
     }
     async_wait<0>();
     if (item_index < 0) {
@@ -1233,17 +1007,6 @@ static int launch_bulk(const SegArgs<T> &a, cudaStream_t stream) {
     return CGNN_OK;
 }
 
-template <typename T, int VW, int LPR>
-static int launch_narrow(const SegArgs<T> &a, cudaStream_t stream) {
-    const int64_t units = ceil_div(a.n_direct, CGNN_SEG_NARROW_RPU) + a.n_items;
-    const int64_t gx = ceil_div(units, CGNN_SEG_NARROW_THREADS / 32);
-    const int64_t gy = ceil_div(a.width, (int64_t)LPR * VW);
-    CGNN_REQUIRE(gx < (1ll << 31) && gy < 65536, "segment reduce: grid too large");
-    seg_narrow_kernel<T, VW, LPR><<<dim3((unsigned)gx, (unsigned)gy), CGNN_SEG_NARROW_THREADS, 0, stream>>>(a);
-    CGNN_LAUNCH_CHECK();
-    return CGNN_OK;
-}
-
 template <typename T, int VW, int LPR, int VPL, bool MASKED, bool GENERIC>
 static int launch_cfg(const SegArgs<T> &a, cudaStream_t stream) {
     constexpr int RPU = CGNN_SEG_RPU < LPR ? CGNN_SEG_RPU : LPR - 1;
@@ -1263,11 +1026,9 @@ static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
 #if CGNN_SEG_ASYNC
     if constexpr (sizeof(T) * VW == 16 && !MASKED && !GENERIC) {
         if (a.seg_mask == nullptr && a.width * (int64_t)sizeof(T) < 0x7fffffffll) {
-#if CGNN_SEG_ASYNC_NARROW
             if (vecs <= 4) return launch_async<T, VW, 4, 1>(a, stream);
             if (vecs <= 8) return launch_async<T, VW, 8, 1>(a, stream);
             if (vecs <= 16) return launch_async<T, VW, 16, 1>(a, stream);
-#endif
             if (vecs >= CGNN_SEG_BULK_MIN_VECS) {
                 if (vecs <= 32 || vecs > CGNN_SEG_ASYNC_MAX_VECS) return launch_async<T, VW, 32, 1>(a, stream);
                 if (vecs <= 64) return launch_async<T, VW, 32, 2>(a, stream);
@@ -1275,19 +1036,6 @@ static int launch_vw(const SegArgs<T> &a, cudaStream_t stream) {
         }
     }
 #endif
-    if constexpr (!MASKED && !GENERIC) {
-#if CGNN_SEG_NARROW
-        // measured on B200 (325 k-node graph, fused vertex pass, single-warp CTAs): side-by-side
-        // groups against one unit per group take 68 -> 58 us at F=16, 128 -> 89 us at F=32 and
-        // 189 -> 138 us at F=64.  Rows masked per group stay on seg_kernel so that both mask modes
-        // add in the same order.
-        if (a.seg_mask == nullptr) {
-            if (vecs <= 4) return launch_narrow<T, VW, 4>(a, stream);
-            if (vecs <= 8) return launch_narrow<T, VW, 8>(a, stream);
-            if (vecs <= 16) return launch_narrow<T, VW, 16>(a, stream);
-        }
-#endif
-    }
 #if CGNN_SEG_BULK
     if constexpr (sizeof(T) * VW == 16) {
         // staged rows: measured faster than register gathers from 17 vectors (272 bytes) up
@@ -1495,89 +1243,136 @@ int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *cons
         copied = true;
     }
     if (copied) CGNN_CUDA(cudaStreamSynchronize(stream));
+    // Pass 1: row lengths (both blocks together), validation, and the row-length histogram (lengths
+    // of HIST_CAP and more share the last bin); median, 99th percentile and maximum are kept with the
+    // plan (cgnn_plan_degrees).
+    constexpr int64_t HIST_CAP = 4096;
+    std::vector<int32_t> deg((size_t)rows);
+    std::vector<int64_t> hist((size_t)HIST_CAP + 1, 0);
+    int64_t longest = 0;
     for (int t = 0; t < p->nterms; ++t) {
-        CGNN_REQUIRE(hp[t][0] == 0, "plan: rowptr[0] must be 0 (term %d)", t);
-        for (int64_t r = 0; r < rows; ++r)
-            CGNN_REQUIRE(hp[t][r + 1] >= hp[t][r], "plan: rowptr not monotone at row %lld (term %d)",
-                         (long long)r, t);
-        CGNN_REQUIRE(hp[t][rows] == p->nnz[t], "plan: rowptr[rows]=%d but nnz=%lld (term %d)",
-                     hp[t][rows], (long long)p->nnz[t], t);
+        const int32_t *rp = hp[t];
+        CGNN_REQUIRE(rp[0] == 0, "plan: rowptr[0] must be 0 (term %d)", t);
+        int64_t bad = -1;
+        for (int64_t r = 0; r < rows; ++r) {
+            const int32_t d = rp[r + 1] - rp[r];
+            if (d < 0 && bad < 0) bad = r;
+            deg[(size_t)r] = t == 0 ? d : deg[(size_t)r] + d;
+        }
+        CGNN_REQUIRE(bad < 0, "plan: rowptr not monotone at row %lld (term %d)", (long long)bad, t);
+        CGNN_REQUIRE(rp[rows] == p->nnz[t], "plan: rowptr[rows]=%d but nnz=%lld (term %d)", rp[rows],
+                     (long long)p->nnz[t], t);
+    }
+    for (int64_t r = 0; r < rows; ++r) {
+        const int64_t d = deg[(size_t)r];
+        ++hist[(size_t)std::min(d, HIST_CAP)];
+        longest = std::max(longest, d);
     }
     const int64_t total = p->nnz[0] + p->nnz[1];
     p->total = total;
+    auto percentile = [&](double q) {
+        const int64_t want = (int64_t)std::ceil(q * (double)rows);
+        int64_t seen = 0;
+        for (int64_t d = 0; d <= HIST_CAP; ++d) {
+            seen += hist[(size_t)d];
+            if (seen >= want) return d;
+        }
+        return HIST_CAP;
+    };
+    p->degree_p50 = rows > 0 ? percentile(0.50) : 0;
+    p->degree_p99 = rows > 0 ? percentile(0.99) : 0;
+    p->degree_max = longest;
     if (split <= 0) {
-        // Degree histogram in one number: rows are short on average -> short chunks keep the
-        // tail of a power-law row small; rows are long on average (bucket segments) ->
-        // longer chunks halve the partial-sum traffic.
+        // Chunk length of the long rows, from the histogram.  Mostly short rows with a thin tail (a
+        // power-law graph block: p99 a few dozen): chunks of 64 keep the tail's work units close to the
+        // direct units in size.  Rows that are long as a rule (bucket segments of an assignment, mean
+        // length above 64) or a heavy tail (one row in a hundred beyond 512 entries): chunks of 128
+        // halve the partial sums that have to be written and added up.
         const double avg = rows > 0 ? (double)total / (double)rows : 0.0;
-        split = avg > 64.0 ? 128 : 64;
+        split = (avg > 64.0 || p->degree_p99 > 512) ? 128 : 64;
     }
     p->split = split;
-    auto degree = [&](int64_t r) {
-        int64_t d = hp[0][r + 1] - hp[0][r];
-        if (p->nterms > 1) d += hp[1][r + 1] - hp[1][r];
-        return d;
-    };
-    int64_t short_nonempty = 0, long_rows = 0;
+
+    // Pass 2: sizes of the work lists.
+    int64_t short_nonempty = 0, long_rows = 0, n_items = 0;
     for (int64_t r = 0; r < rows; ++r) {
-        const int64_t d = degree(r);
-        if (d > split) ++long_rows;
-        else if (d > 0) ++short_nonempty;
+        const int64_t d = deg[(size_t)r];
+        if (d > split) {
+            ++long_rows;
+            n_items += (d + split - 1) / split;
+        } else if (d > 0) {
+            ++short_nonempty;
+        }
     }
     p->compact = rows >= 1024 && short_nonempty * 2 < rows ? 1 : 0;
     const bool identity = !p->compact && long_rows == 0;
-    std::vector<int32_t> dst((size_t)rows, 0), uptr, urow;
-    std::vector<int4> items, longs;
-    int64_t pos = 0;
-    for (int64_t r = 0; r < rows; ++r) {
-        const int64_t d = degree(r);
-        if (d > split || (p->compact && d == 0)) continue;
-        uptr.push_back((int32_t)pos);
-        if (!identity) urow.push_back((int32_t)r);
-        dst[r] = (int32_t)pos;
-        pos += d;
-    }
-    uptr.push_back((int32_t)pos);
-    p->n_direct = (int64_t)uptr.size() - 1;
-    for (int64_t r = 0; r < rows; ++r) {
-        const int64_t d = degree(r);
-        if (d <= split) continue;
-        const int first = (int)items.size();
-        for (int64_t o = 0; o < d; o += split)
-            items.push_back(make_int4((int)longs.size(), (int)(pos + o), (int)(pos + std::min<int64_t>(o + split, d)), 0));
-        longs.push_back(make_int4((int)r, first, (int)items.size() - first, (int)pos));
-        dst[r] = (int32_t)pos;
-        pos += d;
-    }
-    CGNN_REQUIRE(pos == total, "plan: internal entry count mismatch");
-    p->n_long = (int64_t)longs.size();
-    p->n_items = (int64_t)items.size();
+    p->n_direct = p->compact ? short_nonempty : rows - long_rows;
+    p->n_long = long_rows;
+    p->n_items = n_items;
 
-    // One device block holds every array; the small ones go up in one staged copy.
+    // One device block holds every array; the small ones are written straight into a page-locked
+    // stage (slot 0 of the thread's arena; slot 1 takes the two words that come back) and go up in
+    // one copy.
     auto span = [](size_t bytes) { return align_up(std::max<size_t>(bytes, 16), 256); };
     const size_t o_uptr = 0;
-    const size_t o_urow = o_uptr + span(uptr.size() * 4);
-    const size_t o_items = o_urow + span(urow.size() * 4);
-    const size_t o_longs = o_items + span(items.size() * 16);
-    const size_t o_dst = o_longs + span(longs.size() * 16);
-    const size_t o_maxsrc = o_dst + span(dst.size() * 4);  // largest source row of each term, filled by the scatter
+    const size_t o_urow = o_uptr + span(((size_t)p->n_direct + 1) * 4);
+    const size_t o_items = o_urow + span(identity ? 0 : (size_t)p->n_direct * 4);
+    const size_t o_longs = o_items + span((size_t)n_items * 16);
+    const size_t o_dst = o_longs + span((size_t)long_rows * 16);
+    const size_t o_maxsrc = o_dst + span((size_t)rows * 4);  // largest source row of each term, filled by the scatter
     const size_t staged = o_maxsrc + span(2 * 4);
+    std::vector<char> pageable;
+    char *stage = static_cast<char *>(pinned_scratch(staged, 0));
+    if (stage == nullptr) {
+        pageable.resize(staged);
+        stage = pageable.data();
+    }
+    int32_t *const uptr = reinterpret_cast<int32_t *>(stage + o_uptr);
+    int32_t *const urow = reinterpret_cast<int32_t *>(stage + o_urow);
+    int4 *const items = reinterpret_cast<int4 *>(stage + o_items);
+    int4 *const longs = reinterpret_cast<int4 *>(stage + o_longs);
+    int32_t *const dst = reinterpret_cast<int32_t *>(stage + o_dst);
+
+    // Pass 3: the direct list (short rows back to back), then the long rows cut into chunks.
+    int64_t pos = 0, listed = 0;
+    for (int64_t r = 0; r < rows; ++r) {
+        const int64_t d = deg[(size_t)r];
+        dst[r] = 0;
+        if (d > split || (p->compact && d == 0)) continue;
+        uptr[listed] = (int32_t)pos;
+        if (!identity) urow[listed] = (int32_t)r;
+        ++listed;
+        dst[r] = (int32_t)pos;
+        pos += d;
+    }
+    uptr[listed] = (int32_t)pos;
+    CGNN_REQUIRE(listed == p->n_direct, "plan: internal row count mismatch");
+    if (long_rows > 0) {
+        int64_t item = 0, lrow = 0;
+        for (int64_t r = 0; r < rows; ++r) {
+            const int64_t d = deg[(size_t)r];
+            if (d <= split) continue;
+            const int64_t first = item;
+            for (int64_t o = 0; o < d; o += split)
+                items[item++] = make_int4((int)lrow, (int)(pos + o), (int)(pos + std::min<int64_t>(o + split, d)), 0);
+            longs[lrow++] = make_int4((int)r, (int)first, (int)(item - first), (int)pos);
+            dst[r] = (int32_t)pos;
+            pos += d;
+        }
+    }
+    CGNN_REQUIRE(pos == total, "plan: internal entry count mismatch");
+    int32_t fallback_words[2];
+    int32_t *max_source = static_cast<int32_t *>(pinned_scratch(sizeof(fallback_words), 1));
+    if (max_source == nullptr) max_source = fallback_words;
+    max_source[0] = max_source[1] = -1;
+    std::memcpy(stage + o_maxsrc, max_source, 2 * sizeof(int32_t));
     const size_t o_entries = staged;
     const size_t o_vperm = o_entries + span((size_t)total * 4);
     const size_t bytes = o_vperm + (want_vperm ? span((size_t)total * 4) : 0);
-    std::vector<char> stage(staged, 0);
-    auto put = [&](size_t off, const void *src, size_t n) { if (n) std::memcpy(stage.data() + off, src, n); };
-    put(o_uptr, uptr.data(), uptr.size() * 4);
-    put(o_urow, urow.data(), urow.size() * 4);
-    put(o_items, items.data(), items.size() * 16);
-    put(o_longs, longs.data(), longs.size() * 16);
-    put(o_dst, dst.data(), dst.size() * 4);
-    int32_t max_source[2] = {-1, -1};
-    put(o_maxsrc, max_source, sizeof(max_source));
     // Stream-ordered allocation: an assignment refresh builds and drops a plan every few epochs,
     // and cudaMalloc / cudaFree would each stall the whole device.
     p->home = stream;
-    p->pooled = cudaMallocAsync(&p->block, bytes, stream) == cudaSuccess;
+    p->pooled = pool_alloc(&p->block, bytes, stream) == cudaSuccess;
     if (!p->pooled) {
         cudaGetLastError();
         if (cudaMalloc(&p->block, bytes) != cudaSuccess) {
@@ -1588,7 +1383,7 @@ int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *cons
         }
     }
     char *base = reinterpret_cast<char *>(p->block);
-    CGNN_CUDA(cudaMemcpyAsync(base, stage.data(), staged, cudaMemcpyHostToDevice, stream));
+    CGNN_CUDA(cudaMemcpyAsync(base, stage, staged, cudaMemcpyHostToDevice, stream));
     p->uptr = reinterpret_cast<int32_t *>(base + o_uptr);
     p->urow = identity ? nullptr : reinterpret_cast<int32_t *>(base + o_urow);
     p->items = reinterpret_cast<int4 *>(base + o_items);
@@ -1605,12 +1400,26 @@ int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *cons
                                                                p->vperm, reinterpret_cast<int32_t *>(base + o_maxsrc));
         }
         CGNN_LAUNCH_CHECK();
-        CGNN_CUDA(cudaMemcpyAsync(max_source, base + o_maxsrc, sizeof(max_source), cudaMemcpyDeviceToHost, stream));
+        if (want_vperm)
+            CGNN_CUDA(cudaMemcpyAsync(max_source, base + o_maxsrc, 2 * sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
+    }
+    if (!want_vperm && pageable.empty()) {
+        // A plan over an index array (no values): its "columns" are the positions 0 .. nnz-1, so the
+        // source row count is known, and the page-locked stage is handed back with an event behind the
+        // copy instead of a wait -- an assignment refresh then synchronises once, for the bucket count.
+        pinned_scratch_in_use(0, stream);
+        p->source_rows[0] = p->nnz[0];
+        p->source_rows[1] = 0;
+        return CGNN_OK;
     }
     // the staged host buffer must outlive the copy
     CGNN_CUDA(cudaStreamSynchronize(stream));
-    p->source_rows[0] = (int64_t)max_source[0] + 1;
-    p->source_rows[1] = (int64_t)max_source[1] + 1;
+    if (want_vperm) {
+        p->source_rows[0] = (int64_t)max_source[0] + 1;
+        p->source_rows[1] = (int64_t)max_source[1] + 1;
+    } else {
+        p->source_rows[0] = p->nnz[0];
+    }
     return CGNN_OK;
 }
 
@@ -1761,6 +1570,15 @@ int cgnn_plan_info(const cgnn_plan *p, int64_t info[8]) {
     info[5] = p->n_direct;
     info[6] = p->nterms;
     info[7] = p->compact;
+    return CGNN_OK;
+}
+
+int cgnn_plan_degrees(const cgnn_plan *p, int64_t out[4]) {
+    CGNN_REQUIRE(p != nullptr && out != nullptr, "plan degrees: null argument");
+    out[0] = p->degree_p50;
+    out[1] = p->degree_p99;
+    out[2] = p->degree_max;
+    out[3] = p->split;
     return CGNN_OK;
 }
 

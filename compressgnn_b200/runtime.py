@@ -65,6 +65,9 @@ class SegmentPlan:
         need = (ctypes.c_int64 * 2)()
         check(lib().cgnn_plan_source_rows(handle, need))
         self.source_rows = (int(need[0]), int(need[1]))  # rows each source matrix must have
+        hist = (ctypes.c_int64 * 4)()
+        check(lib().cgnn_plan_degrees(handle, hist))
+        self.degree_p50, self.degree_p99, self.degree_max = int(hist[0]), int(hist[1]), int(hist[2])
 
     @property
     def handle(self):

@@ -69,6 +69,12 @@ void cgnn_plan_destroy(cgnn_plan *plan);
  * list, terms, 1 if empty rows are left out of the list. */
 int cgnn_plan_info(const cgnn_plan *plan, int64_t info[8]);
 
+/* out[0..3] = median, 99th percentile and maximum of the row lengths (entries per output row, both
+ * blocks together; the percentiles saturate at 4096) and the chunk length chosen from them: rows
+ * longer than the chunk length are cut into chunks that run as work units of their own.
+ * (The reference picks its kernel from nnz and the width alone, layer/CompressgnnSPMM.py:14-19.) */
+int cgnn_plan_degrees(const cgnn_plan *plan, int64_t out[4]);
+
 /* rows[t] = 1 + the largest source row that block t of the plan refers to (0 when the block has
  * no entries).  The SpMM entry points take raw pointers and cannot see how many rows `src`
  * has: a caller passes only matrices with at least this many rows.  (The reference's kernels

@@ -168,6 +168,23 @@ def test_sources_and_outputs_are_checked_on_the_host(rt):
     assert rt.device_status() == 0
 
 
+def test_plan_records_the_row_length_histogram(rt):
+    """The chunk length follows the row-length histogram: short rows with a thin tail get chunks of 64,
+    rows that are long as a rule (or a heavy tail) chunks of 128."""
+    rng = np.random.default_rng(5)
+    rp, col = random_csr(rng, 4000, 900, 6, long_rows=[(10, 700)])
+    thin = rt.SegmentPlan.from_csr(cu(rp), cu(col))
+    lengths = np.diff(rp)
+    assert thin.degree_max == 700 and thin.degree_p50 == int(np.sort(lengths)[len(lengths) // 2 - 1 + len(lengths) % 2])
+    assert thin.degree_p99 < 64 and thin.split == 64 and thin.long_rows == 1
+    rp, col = random_csr(rng, 300, 900, 200, empty_frac=0.0)
+    long_rows = rt.SegmentPlan.from_csr(cu(rp), cu(col))
+    assert long_rows.degree_p50 > 64 and long_rows.split == 128
+    rp, col = random_csr(rng, 2000, 5000, 4, long_rows=[(i, 600 + i) for i in range(0, 2000, 40)])
+    heavy_tail = rt.SegmentPlan.from_csr(cu(rp), cu(col))
+    assert heavy_tail.degree_p99 > 512 and heavy_tail.split == 128
+
+
 def test_fused_pair_matches_two_calls(rt):
     rng = np.random.default_rng(21)
     rows, n0, n1, width = 700, 400, 650, 96
