@@ -709,6 +709,10 @@ __device__ __forceinline__ void async_copy16(uint32_t dst_shared, const void *sr
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_shared), "l"(src) : "memory");
 }
 __device__ __forceinline__ void async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// Steps (warp-wide copies per vector) of one stage: a stage never holds more than the 32 entries of a window.
+__host__ __device__ constexpr int async_steps(int lpr) {
+    return CGNN_SEG_ASYNC_K * (32 / lpr) > 32 ? 32 / (32 / lpr) : CGNN_SEG_ASYNC_K;
+}
 template <int N>
 __device__ __forceinline__ void async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -727,7 +731,7 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
     static_assert(sizeof(T) * VW == 16, "cp.async staging moves 16-byte vectors");
     static_assert(LPR == 32 || VPL == 1, "several vectors per lane only for full-warp rows");
     constexpr int G = 32 / LPR;               // entries per step (one warp-wide copy per vector)
-    constexpr int K = CGNN_SEG_ASYNC_K, S = CGNN_SEG_ASYNC_S, RPU = LPR == 32 ? CGNN_SEG_ASYNC_RPU : CGNN_SEG_NARROW_RPU;
+    constexpr int K = async_steps(LPR), S = CGNN_SEG_ASYNC_S, RPU = LPR == 32 ? CGNN_SEG_ASYNC_RPU : CGNN_SEG_NARROW_RPU;
     constexpr int KE = K * G;                 // entries per stage
     static_assert(32 % KE == 0, "a stage must not straddle two entry windows");
     constexpr int TILE = LPR * VPL * VW;      // columns of one tile
@@ -883,6 +887,15 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
         if (cnt >= KE && ebase + KE <= row_end && ebase < row_end) {  // a full stage inside the current row
 #pragma unroll
             for (int j = 0; j < K; ++j) fma_row<T, VW, VPL>(acc, x[j], __shfl_sync(FULL, v, pos + j * G), colok);
+        } else if constexpr (G == 1) {  // one entry per step: finish the rows that end before it, then add it
+#pragma unroll
+            for (int j = 0; j < K; ++j) {
+                const T w = __shfl_sync(FULL, v, (pos + j) & 31);
+                if (j < cnt) {
+                    while (ebase + j >= row_end) flush();
+                    fma_row<T, VW, VPL>(acc, x[j], w, colok);
+                }
+            }
         } else {
             const int stage_end = ebase + min(cnt, KE);
 #pragma unroll
@@ -953,7 +966,7 @@ __global__ void __launch_bounds__(32) seg_async_kernel(const SegArgs<T> a) {
 
 template <typename T, int VW, int LPR, int VPL, bool PLAIN>
 static int launch_async_as(const SegArgs<T> &a, cudaStream_t stream) {
-    constexpr size_t BYTES = (size_t)CGNN_SEG_ASYNC_S * CGNN_SEG_ASYNC_K * 32 * VPL * 16;
+    constexpr size_t BYTES = (size_t)CGNN_SEG_ASYNC_S * async_steps(LPR) * 32 * VPL * 16;
     constexpr int RPU = LPR == 32 ? CGNN_SEG_ASYNC_RPU : CGNN_SEG_NARROW_RPU;
     static std::mutex mu;
     static uint64_t configured = 0;  // one bit per device: the kernel may use BYTES of shared memory
