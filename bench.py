@@ -383,13 +383,27 @@ def run_gpu(args):
         ms = float(t.item())
     ms_per_step = ms / args.steps
 
-    # per-launch durations (events recorded inside the timed region)
-    per_launch = {}
-    for rec in records:
-        for name, e0, e1 in rec:
-            per_launch.setdefault(name, []).append(e0.elapsed_time(e1))
-    launch_ms = {k: float(np.mean(v)) for k, v in per_launch.items()}
+    # Durations of the two fused vertex passes: events recorded inside the timed region (a pass is one
+    # native call, split in two around its last launch so that the events can sit between them).
+    def mean_ms(recs):
+        per_launch = {}
+        for rec in recs:
+            for name, e0, e1 in rec:
+                per_launch.setdefault(name, []).append(e0.elapsed_time(e1))
+        return {k: float(np.mean(v)) for k, v in per_launch.items()}
+
+    launch_ms = mean_ms(records)
     bytes_by_name = dict(fwd_bytes + bwd_bytes)
+    # The six-launch table comes from a second pass of the same steps in which every block is issued
+    # by a call of its own with events around it (slower on the host, same kernels).
+    detail = []
+    for _ in range(args.steps):
+        rec = []
+        spmm_layer._forward(graph, x, rec, per_block=True)
+        spmm_layer._backward(graph, grad, rec, per_block=True)
+        detail.append(rec)
+    torch.cuda.synchronize()
+    detail_ms = mean_ms(detail)
 
     # the GPU's results against the CPU leg's, same inputs (N=1)
     parity = None
@@ -475,8 +489,9 @@ def run_gpu(args):
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_src, "traffic": traffic, "traffic_source": traffic_src,
                      "algorithmic_bytes_per_launch": bytes_by_name[dom], "ms_per_launch": launch_ms[dom],
-                     "launches": {k: {"ms": launch_ms[k], "algorithmic_GBps": bytes_by_name[k] / launch_ms[k] / 1e6}
-                                  for k in launch_ms}},
+                     "launches": {k: {"ms": detail_ms[k], "algorithmic_GBps": bytes_by_name[k] / detail_ms[k] / 1e6}
+                                  for k in detail_ms},
+                     "launches_source": "second pass of the same steps, one call and one event pair per block"},
         "clocks": clocks.summary(),
     }
     if world > 1 and args.scaling == "strong":

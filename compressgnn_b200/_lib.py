@@ -34,6 +34,9 @@ SIGNATURES = {
     "cgnn_spmm_static_scratch": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr]),
     "cgnn_spmm_pair": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
                                 _c_ptr, _c_size, _c_ptr]),
+    "cgnn_propagate": (_c_int, [_c_int, ctypes.POINTER(_c_ptr), ctypes.POINTER(_c_ptr), ctypes.POINTER(_c_ptr),
+                                ctypes.POINTER(_c_size), _c_int, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int,
+                                _c_int, _c_ptr]),
     "cgnn_plan_permute_values": (_c_int, [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
     "cgnn_cluster_project": (_c_int, [_c_int, _c_ptr, _c_ptr, _c_i64, _c_i64, _c_int, _c_ptr,
                                       _c_ptr]),

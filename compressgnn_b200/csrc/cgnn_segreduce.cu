@@ -1652,6 +1652,38 @@ int cgnn_spmm_pair(const cgnn_plan *plan, int dtype, int64_t width, const void *
                scratch, scratch_bytes, (cudaStream_t)stream);
 }
 
+int cgnn_propagate(int n_launches, const cgnn_plan *const *plans, const void *const *vals,
+                   void *const *scratch, const size_t *scratch_bytes, int dtype, int64_t width,
+                   const void *x, void *rule_out, void *out, int rule_term_of_last, int first,
+                   int last, cgnn_stream_t stream_) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    CGNN_REQUIRE(n_launches >= 2, "propagate: a pass has at least the rule launch and the vertex launch");
+    CGNN_REQUIRE(plans != nullptr && vals != nullptr && scratch != nullptr && scratch_bytes != nullptr,
+                 "propagate: null launch table");
+    CGNN_REQUIRE(rule_term_of_last == 0 || rule_term_of_last == 1, "propagate: rule_term_of_last must be 0 or 1");
+    for (int i = 0; i < n_launches; ++i) {
+        CGNN_REQUIRE(plans[i] != nullptr, "propagate: null plan of launch %d", i);
+        CGNN_REQUIRE(plans[i]->nterms == (i == n_launches - 1 ? 2 : 1), "propagate: launch %d has the wrong kind of plan", i);
+    }
+    first = std::max(first, 0);
+    last = std::min(last, n_launches - 1);
+    for (int i = first; i <= last; ++i) {
+        int rc;
+        if (i == 0)
+            rc = run(plans[0], dtype, width, vals[0], x, nullptr, nullptr, nullptr, nullptr, rule_out, 0,
+                     scratch[0], scratch_bytes[0], stream);
+        else if (i < n_launches - 1)
+            rc = run(plans[i], dtype, width, vals[i], rule_out, nullptr, nullptr, nullptr, nullptr, rule_out, 1,
+                     scratch[i], scratch_bytes[i], stream);
+        else
+            rc = run(plans[i], dtype, width, vals[i], rule_term_of_last == 0 ? rule_out : x,
+                     rule_term_of_last == 0 ? x : rule_out, nullptr, nullptr, nullptr, out, 0, scratch[i],
+                     scratch_bytes[i], stream);
+        if (rc != CGNN_OK) return rc;
+    }
+    return CGNN_OK;
+}
+
 int cgnn_cluster_mean(const cgnn_plan *plan, int dtype, int64_t width, const void *x,
                       const int32_t *count, void *out, void *scratch, size_t scratch_bytes,
                       cgnn_stream_t stream) {

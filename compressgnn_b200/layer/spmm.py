@@ -43,9 +43,34 @@ def _rule_buffer(graph, like, given):
     return given
 
 
-def _forward(graph, x, record=None, out=None, rule_out=None):
+def _whole_pass(graph, x, backward, record, out, rule_out):
+    """One direction in one native call (two when ``record`` asks for the time of the vertex pass)."""
+    plan = graph.propagation_plan()
+    table = plan.whole_pass(backward, x.size(1), x.dtype)
+    rule_out = _rule_buffer(graph, x, rule_out)
+    if out is None:
+        out = torch.empty((graph.vertex_cnt, x.size(1)), dtype=x.dtype, device=x.device)
+    elif out.shape != (graph.vertex_cnt, x.size(1)) or out.dtype != x.dtype or not out.is_contiguous():
+        raise RuntimeError("out does not match the graph and the feature matrix")
+    if out.numel() == 0:
+        return out
+    with torch.cuda.device(x.device):
+        if record is None:
+            return _native.propagate_pass(table, x, rule_out, out)
+        last = table["n"] - 1
+        _native.propagate_pass(table, x, rule_out, out, 0, last - 1)
+        return _timed(record, "bwd_out" if backward else "fwd_out",
+                      lambda: _native.propagate_pass(table, x, rule_out, out, last, last))
+
+
+def _forward(graph, x, record=None, out=None, rule_out=None, per_block=False):
+    """``out = A_hat^T x``.  ``record`` (a list) receives ``(name, start, stop)`` CUDA events: around the
+    fused vertex pass only, or -- with ``per_block`` -- around every launch, each issued by a call of
+    its own (the benchmark's per-kernel table)."""
     _require_cuda(x)
     x = x.contiguous()
+    if not per_block:
+        return _whole_pass(graph, x, False, record, out, rule_out)
     plan = graph.propagation_plan()
     dt = x.dtype
     # rule_out is placed a whole number of rows away from x so that the fused pass over
@@ -60,9 +85,11 @@ def _forward(graph, x, record=None, out=None, rule_out=None):
         plan.out, graph.v2r_graph.value_as(dt), rule_out, graph.v2v_graph.value_as(dt), x, out=out))
 
 
-def _backward(graph, grad, record=None, out=None, rule_out=None):
+def _backward(graph, grad, record=None, out=None, rule_out=None, per_block=False):
     _require_cuda(grad)
     grad = grad.contiguous()
+    if not per_block:
+        return _whole_pass(graph, grad, True, record, out, rule_out)
     plan = graph.propagation_plan()
     dt = grad.dtype
     rule_out = _rule_buffer(graph, grad, rule_out)

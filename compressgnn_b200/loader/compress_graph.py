@@ -31,6 +31,43 @@ class PropagationPlan:
         self.v2r_t = SegmentPlan.from_csr(*g.v2r_graph.csc()[:2])
         self.levels_t = [SegmentPlan.from_csr(*lvl.csc()[:2]) for lvl in g.r2r_graph]
         self.out_t = SegmentPlan.from_csr(*g.v2v_graph.csc()[:2], *g.r2v_graph.csc()[:2])
+        self._graph = g
+        self._passes = {}
+
+    def whole_pass(self, backward, width, dtype):
+        """The launch table of one direction as ``cgnn_propagate`` takes it (plans, values in plan
+        order, scratch), built once per (direction, width, dtype, stream) and then reused: a pass is
+        one native call."""
+        import ctypes
+        from ..runtime import _dtype_code_of, _stream_ptr
+        stream = _stream_ptr(self.device)
+        key = (bool(backward), int(width), dtype, stream)
+        table = self._passes.get(key)
+        if table is None:
+            g = self._graph
+            if backward:
+                plans = [self.v2r_t] + list(reversed(self.levels_t)) + [self.out_t]
+                values = [g.v2r_graph.value_as(dtype, True)] + \
+                         [lvl.value_as(dtype, True) for lvl in reversed(g.r2r_graph)]
+                last = (g.v2v_graph.value_as(dtype, True), g.r2v_graph.value_as(dtype, True))
+            else:
+                plans = [self.r2v] + list(self.levels) + [self.out]
+                values = [g.r2v_graph.value_as(dtype)] + [lvl.value_as(dtype) for lvl in g.r2r_graph]
+                last = (g.v2r_graph.value_as(dtype), g.v2v_graph.value_as(dtype))
+            code = _dtype_code_of(dtype)
+            ordered = [p.values(v) for p, v in zip(plans[:-1], values)] + [plans[-1].values(*last)]
+            scratch = [p.scratch(width, code) for p in plans]
+            n = len(plans)
+            table = dict(
+                n=n, code=code, keep=(plans, ordered),  # the tensors behind the raw pointers stay alive here
+                plans=(ctypes.c_void_p * n)(*[p.handle.value for p in plans]),
+                vals=(ctypes.c_void_p * n)(*[t.data_ptr() if t.numel() else None for t in ordered]),
+                scratch=(ctypes.c_void_p * n)(*[s[0].value for s in scratch]),
+                scratch_bytes=(ctypes.c_size_t * n)(*[s[1] for s in scratch]),
+                rule_term=1 if backward else 0, stream=stream,
+                source_rows=(plans[0].source_rows[0], plans[-1].source_rows))
+            self._passes[key] = table
+        return table
 
 
 class CompressGraph:

@@ -45,6 +45,14 @@ def _dtype_code(t, what="tensor"):
     raise RuntimeError(f"{what}: only float32 and float64 are supported")
 
 
+def _dtype_code_of(dtype):
+    if dtype == torch.float32:
+        return 0
+    if dtype == torch.float64:
+        return 1
+    raise RuntimeError("only float32 and float64 are supported")
+
+
 def _require(cond, msg):
     if not cond:
         raise RuntimeError(msg)
@@ -264,6 +272,21 @@ def spmm_pair_with_plan(plan, value0, mat0, value1, mat1, out=None, accumulate=F
         check(lib().cgnn_spmm_pair(plan.handle, code, width, _ptr(value), _ptr(mat0), _ptr(mat1),
                                    _ptr(out), 1 if accumulate else 0, sp, sb,
                                    _stream_ptr(mat0.device)))
+    return out
+
+
+def propagate_pass(table, x, rule_out, out, first=0, last=None):
+    """Issue the launches ``first .. last`` of one propagation direction (``table`` from
+    ``PropagationPlan.whole_pass``) in one native call: rules gather from ``x`` into ``rule_out``, the
+    rule levels run in place, the fused vertex pass writes ``out``."""
+    n_rules, (need0, need1) = table["source_rows"]
+    rule_side, x_side = (need0, need1) if table["rule_term"] == 0 else (need1, need0)
+    _require(x.size(0) >= max(n_rules, x_side) and rule_out.size(0) >= rule_side,
+             "propagate: the graph refers to rows beyond the feature or rule matrix")
+    check(lib().cgnn_propagate(table["n"], table["plans"], table["vals"], table["scratch"], table["scratch_bytes"],
+                               table["code"], x.size(1), x.data_ptr(), rule_out.data_ptr() if rule_out.numel() else None,
+                               out.data_ptr(), table["rule_term"], first, table["n"] - 1 if last is None else last,
+                               table["stream"]))
     return out
 
 

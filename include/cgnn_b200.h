@@ -146,6 +146,24 @@ int cgnn_spmm_pair(const cgnn_plan *plan, int dtype, int64_t width, const void *
                    const void *src0, const void *src1, void *out, int accumulate,
                    void *scratch, size_t scratch_bytes, cgnn_stream_t stream);
 
+/* One direction of the compressed propagation in ONE call: the launch sequence of the reference's
+ * Compressgnn_SPMM_Function (ref: layer/CompressgnnSPMM.py:47-60 forward, :65-85 backward), issued
+ * back to back on `stream` without returning to the host language in between.
+ *   launch 0            rule_out  = A[0] x                      (rules gather vertices: r2v, or v2r^T)
+ *   launch 1 .. n-2     rule_out += A[i] rule_out               (the rule levels, in place)
+ *   launch n-1          out       = pair(A[n-1]) (s0, s1)       (the fused two-block vertex pass)
+ * where (s0, s1) = (rule_out, x) when rule_term_of_last is 0 (forward: v2r | v2v) and (x, rule_out)
+ * when it is 1 (backward: v2v^T | r2v^T).  plans[i] / vals[i] (values in plan order, or NULL for
+ * ones) / scratch[i] / scratch_bytes[i] describe launch i as for cgnn_spmm and cgnn_spmm_pair.
+ * Only the launches first <= i <= last are issued, so that a caller can time one of them between
+ * two calls.  The host language pays its call overhead once per pass instead of once per block: with
+ * the feature columns sharded over several GPUs a block's kernel takes 15-80 us, less than an
+ * interpreter needs to issue it. */
+int cgnn_propagate(int n_launches, const cgnn_plan *const *plans, const void *const *vals,
+                   void *const *scratch, const size_t *scratch_bytes, int dtype, int64_t width,
+                   const void *x, void *rule_out, void *out, int rule_term_of_last, int first,
+                   int last, cgnn_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------
  * LSH cluster assignment.
  * ref: cluster_assign_cuda, src/runtime/csrc/cluster/cuda/cluster_kernel.cu:118-153;
