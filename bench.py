@@ -312,6 +312,34 @@ def build_graph_once(name, world, rank):
     return built
 
 
+def reference_cuda_leg(graph, x, grad, our_step, steps, e_orig, width_total):
+    """Time the reference's CUDA kernels (oracle/_ref_cuda) on the resident inputs and compare their
+    results with ours.  Returns the fields of the informational `reference_cuda` block, or None when the
+    module is absent or the matrix is too large for the 32-bit index products of those kernels."""
+    import torch
+    from oracle import oracle
+    module = oracle.reference_cuda_module()
+    if module is None or max(graph.vertex_cnt, graph.rule_cnt) * x.size(1) >= 2 ** 31:
+        return None
+    for _ in range(3):
+        ref_out, ref_gx = oracle.reference_cuda_step(module, graph, x, grad)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        ref_out, ref_gx = oracle.reference_cuda_step(module, graph, x, grad)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / steps
+    out, gx = our_step()
+    return {"ms_per_step": ms, "value": 2 * e_orig * width_total / (ms * 1e-3) / 1e9, "unit": UNIT,
+            "what": "the reference's own CUDA kernels (src/runtime/csrc/sparse/cuda) compiled for sm_100, launched "
+                    "in the order and with the method choice of layer/CompressgnnSPMM.py:14-19,54-60,80-85; "
+                    "informational, not the reference arm",
+            "max_scaled_error_forward_vs_ours": scaled_error(out.cpu(), ref_out.cpu()),
+            "max_scaled_error_backward_vs_ours": scaled_error(gx.cpu(), ref_gx.cpu())}
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -452,6 +480,12 @@ def run_gpu(args):
         assert torch.equal(out_host, step()[0].cpu()), "host front end and resident path disagree"
         del pipe, x_pin, g_pin, out_host, gx_host
 
+    # For context only (never a ratio's denominator): the reference's own CUDA kernels, compiled for
+    # sm_100, on the same graph and inputs, launched as the reference's GPU branches launch them.
+    ref_cuda = None
+    if rank == 0 and world == 1 and not args.no_reference_cuda:
+        ref_cuda = reference_cuda_leg(graph, x, grad, step, args.steps, e_orig, width_total)
+
     rt.raise_on_device_status()
     del x, grad
 
@@ -503,6 +537,8 @@ def run_gpu(args):
         line["strong_scaling_ceiling_by_bytes"] = one_gpu / (world * shard_bytes)
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if ref_cuda is not None:
+        line["reference_cuda"] = ref_cuda
     if parity is not None:
         line["parity_checked"] = parity
     if extra:
@@ -885,6 +921,8 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=3, help="steps of the CPU baseline leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-reference-cuda", action="store_true",
+                    help="skip the informational leg that times the reference's own CUDA kernels")
     ap.add_argument("--no-extra", action="store_true", help="skip the cluster and GCN legs reported under `extra`")
     args = ap.parse_args()
     if args.workload == "cluster":

@@ -262,3 +262,49 @@ def reference_propagation(blocks, x, grad, n, r, threads=None):
         rule_g = spmm_ref(t(transpose_csr(*level, r)), rule_g, rule_g)
     gx = spmm_ref(t(transpose_csr(*blocks["r2v"], n)), rule_g, spmm_ref(t(transpose_csr(*blocks["v2v"], n)), gt))
     return out.numpy(), gx.numpy(), "reference"
+
+
+def reference_cuda_module():
+    """The reference's runtime built WITH its CUDA kernels (``oracle/_ref_cuda``, see
+    ``build_ref.build_runtime_cuda``; module name ``compressgnn_runtime_cuda`` so that it can sit
+    beside the CPU build), or ``None`` when it is absent."""
+    ref_dir = HERE / "_ref_cuda"
+    if not (ref_dir / "compressgnn_runtime_cuda.so").is_file():
+        return None
+    if str(ref_dir) not in sys.path:
+        sys.path.insert(0, str(ref_dir))
+    try:
+        import torch  # noqa: F401  (libtorch symbols must be loaded first)
+        return __import__("compressgnn_runtime_cuda")
+    except ImportError:
+        return None
+
+
+def reference_cuda_step(rt, graph, x, grad):
+    """One forward and one backward compressed propagation by the reference's own CUDA kernels, launched
+    as its GPU branches launch them (layer/CompressgnnSPMM.py:14-19 method choice, :54-60 forward,
+    :80-85 backward).  ``graph`` is a CompressGraph on the device, ``x`` / ``grad`` device matrices.
+
+    The kernels form ``elist * col_num`` and ``row * col_num`` in 32-bit integers
+    (sparse/cuda/row_balance.cuh:82-128, nnz_balance.cuh:145-200): callers stay below 2^31 elements."""
+    rows = max(graph.vertex_cnt, graph.rule_cnt)
+    if rows * x.size(1) >= 2 ** 31:
+        raise ValueError("the reference's CUDA kernels index with 32-bit products: matrix too large")
+
+    def gpu_spmm(blk, m, out, prefer_row=False):
+        method = "rowbalance_rowcache" if (prefer_row and blk[1].numel() >= 1000000 and m.size(-1) >= 64) \
+            else "nnzbalance_rowcache"
+        return rt.spmm_func(blk[0], blk[1], blk[2], m, method, out)
+
+    g = graph
+    rule_out = gpu_spmm(g.r2v_graph.csr(), x, None, prefer_row=True)
+    for level in g.r2r_graph:
+        rule_out = gpu_spmm(level.csr(), rule_out, rule_out)
+    out = gpu_spmm(g.v2r_graph.csr(), rule_out, None)
+    out = gpu_spmm(g.v2v_graph.csr(), x, out, prefer_row=True)
+    rule_g = gpu_spmm(g.v2r_graph.csc(), grad, None)
+    for level in reversed(g.r2r_graph):
+        rule_g = gpu_spmm(level.csc(), rule_g, rule_g)
+    gx = gpu_spmm(g.v2v_graph.csc(), grad, None, prefer_row=True)
+    gx = gpu_spmm(g.r2v_graph.csc(), rule_g, gx, prefer_row=True)
+    return out, gx

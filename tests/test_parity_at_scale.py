@@ -59,6 +59,24 @@ def test_propagation_workload_against_reference_cpu(web_graph, width):
     assert rt.device_status() == 0
 
 
+def test_propagation_workload_against_reference_cuda_kernels(web_graph):
+    """The reference's own CUDA kernels (compiled for sm_100 into oracle/_ref_cuda) on the same graph and
+    inputs: a second checker.  They add with float atomics in no fixed order, so the comparison is by
+    tolerance; 256 columns keep every 32-bit index product of theirs below 2^31."""
+    from compressgnn_b200.layer import spmm as spmm_layer
+    ref = oracle.reference_cuda_module()
+    if ref is None:
+        pytest.skip("oracle/_ref_cuda is not built")
+    graph, _blocks, _ = web_graph
+    n, width = graph.vertex_cnt, 256
+    gen = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn(n, width, device="cuda", generator=gen)
+    grad = torch.randn(n, width, device="cuda", generator=gen)
+    ref_out, ref_gx = oracle.reference_cuda_step(ref, graph, x, grad)
+    assert_close_rel(spmm_layer._forward(graph, x).cpu().numpy(), ref_out.cpu().numpy(), what="forward vs reference CUDA")
+    assert_close_rel(spmm_layer._backward(graph, grad).cpu().numpy(), ref_gx.cpu().numpy(), what="backward vs reference CUDA")
+
+
 def _codes(x, planes):
     """Raw sign codes through the C ABI (what cluster_assign compacts)."""
     from compressgnn_b200 import runtime as rt
