@@ -676,6 +676,22 @@ def measure_cluster(n, steps, warmup, with_cpu=True):
         ms = timed(fn)
         op_report[name] = {"ms": ms, "algorithmic_bytes": nbytes, "algorithmic_GBps": nbytes / ms / 1e6,
                            "frac_of_peak": nbytes / ms / 1e6 / peak}
+    # For context: the same operators by the reference's own CUDA kernels (oracle/_ref_cuda) on the same
+    # tensors -- its assignment through a library GEMM and a 2^bits histogram, its means and the
+    # reconstruct backward through float atomics, its gather/scatter kernels one element per thread.
+    from oracle import oracle
+    ref = oracle.reference_cuda_module()
+    if ref is not None and n * out_width < 2 ** 31:
+        rws = ref.cluster_workspace(xd, bits)
+        ref_ops = {
+            "cluster_assign (projection+codes+compaction)": lambda: ref.cluster_assign(xd, cluster.random_vectors, bits, rws),
+            "cluster_mean": lambda: ref.cluster_mean(xd, ids, counts),
+            "cluster_mean_backward": lambda: ref.cluster_mean_backward(g_small, ids, counts),
+            "cluster_reconstruct (bias+relu)": lambda: ref.cluster_reconstruct(table, ids, bias, True),
+            "cluster_reconstruct_backward (relu, exact mask)": lambda: ref.cluster_reconstruct_backward(grad_out, ids, y, groups, True),
+        }
+        for name, fn in ref_ops.items():
+            op_report[name]["reference_cuda_ms"] = timed(fn, 10)
     rt.raise_on_device_status()
     # the operator that moves the most bytes per epoch is the roofline's subject
     dom = "cluster_reconstruct (bias+relu)"

@@ -395,6 +395,7 @@ struct HostSegments {
     std::mutex lock;
     const void *workspace = nullptr;
     int64_t n = 0, valid = 0;
+    bool on_device = false;            // start[16 ..] holds the plan's row statistics instead of segment starts
     int32_t *start = nullptr;          // page-locked, grow-only (the copy into it must not be staged)
     size_t capacity = 0;               // in words
     std::vector<int32_t> pageable;     // used when page-locked memory cannot be had
@@ -511,14 +512,28 @@ int cgnn_cluster_assign(const int32_t *codes, int64_t n, int bits, void *workspa
     scatter_ids_kernel<<<grid_for(n), 256, 0, stream>>>(L.vals[0], L.cid, flags, n, ids, L.segstart,
                                                         L.active);
     CGNN_LAUNCH_CHECK();
-    // One synchronisation fetches `active` and, speculatively, the head of the segment-start
-    // array (active <= 2^bits, so 2^bits + 2 entries cover it for the usual bit counts); the
-    // export step then needs no further round trip.
+    // One synchronisation fetches `active`.  With it comes what the export step needs to build the
+    // bucket plan without another round trip: when the buckets are few enough for one CTA to scan
+    // (at most 2^20: the usual bit counts), the row statistics of the plan, taken on the device and
+    // written behind `active`; otherwise, speculatively, the head of the segment-start array.
     HostSegments &hs = host_segments();
     std::lock_guard<std::mutex> guard(hs.lock);
-    const int64_t want = std::min<int64_t>(n + 2, std::min<int64_t>(((int64_t)1 << bits) + 2, (int64_t)1 << 20));
     hs.workspace = workspace;
     hs.n = n;
+    hs.valid = 0;
+    hs.on_device = std::min<int64_t>(n, (int64_t)1 << bits) + 1 <= PLAN_DEVICE_MAX_ROWS;
+    if (hs.on_device) {
+        int32_t *header_dev = L.active + 16;  // inside the 256-byte slot of `active`
+        rc = plan_stats_on_device(L.segstart, L.active, n, 0, header_dev, stream);
+        if (rc != CGNN_OK) return rc;
+        int32_t *host = hs.reserve(16 + PLAN_HEADER_WORDS);
+        CGNN_CUDA(cudaMemcpyAsync(host, L.active, sizeof(int32_t) * (16 + PLAN_HEADER_WORDS), cudaMemcpyDeviceToHost,
+                                  stream));
+        CGNN_CUDA(cudaStreamSynchronize(stream));
+        *active_out = host[0];
+        return CGNN_OK;
+    }
+    const int64_t want = std::min<int64_t>(n + 2, std::min<int64_t>(((int64_t)1 << bits) + 2, (int64_t)1 << 20));
     int32_t *host = hs.reserve((size_t)want + 1);  // [0] receives `active`, the segment starts follow
     CGNN_CUDA(cudaMemcpyAsync(host, L.active, sizeof(int32_t), cudaMemcpyDeviceToHost, stream));
     CGNN_CUDA(cudaMemcpyAsync(host + 1, L.segstart, sizeof(int32_t) * (size_t)want,
@@ -556,8 +571,12 @@ int cgnn_cluster_assign_export(const void *workspace, int64_t n, int64_t active,
     {
         HostSegments &hs = host_segments();
         std::lock_guard<std::mutex> guard(hs.lock);
-        const bool have = hs.workspace == workspace && hs.n == n && hs.valid == active + 2;
-        rc = plan_build(p, rp, cl, split, stream, have ? hs.start + 1 : nullptr, false);
+        if (hs.workspace == workspace && hs.n == n && hs.on_device && split == 0 && hs.start[0] == active) {
+            rc = plan_fill_on_device(p, L.segstart, L.vals[0], hs.start + 16, stream);
+        } else {
+            const bool have = hs.workspace == workspace && hs.n == n && !hs.on_device && hs.valid == active + 2;
+            rc = plan_build(p, rp, cl, split, stream, have ? hs.start + 1 : nullptr, false);
+        }
     }
     if (rc != CGNN_OK) {
         cgnn_plan_destroy(p);

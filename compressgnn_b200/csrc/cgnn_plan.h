@@ -46,6 +46,24 @@ namespace cgnn {
 int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *const col[2], int split,
                cudaStream_t stream, const int32_t *host_rowptr0 = nullptr, bool want_vperm = true);
 
+// The same plan built WITHOUT host loops, for blocks whose row pointers only exist on the device (the
+// bucket plan of an assignment refresh), in two steps around the caller's one synchronisation:
+//   plan_stats_on_device   (queued before the wait) reads the row count from device memory, takes the
+//                          row-length histogram, chooses the chunk length and counts the work lists;
+//                          the figures land in header[0 .. PLAN_HEADER_WORDS), which the caller copies
+//                          to the host together with whatever else it waits for;
+//   plan_fill_on_device    (after the wait, header on the host) allocates the plan and lets kernels
+//                          write its lists and entries; no further wait, no host-side pass over the rows.
+// Rows are limited to PLAN_DEVICE_MAX_ROWS (one CTA scans them); the block has no values.
+constexpr int PLAN_HEADER_WORDS = 16;
+constexpr int64_t PLAN_DEVICE_MAX_ROWS = 1 << 20;
+enum PlanHeader { PH_ROWS = 0, PH_SPLIT, PH_COMPACT, PH_IDENTITY, PH_DIRECT, PH_LONG, PH_ITEMS, PH_P50, PH_P99,
+                  PH_MAX, PH_SHORT_ENTRIES, PH_VALID };
+int plan_stats_on_device(const int32_t *rowptr, const int32_t *last_row_dev, int64_t nnz, int split,
+                         int32_t *header_dev, cudaStream_t stream);
+int plan_fill_on_device(cgnn_plan *p, const int32_t *rowptr, const int32_t *col, const int32_t *header_host,
+                        cudaStream_t stream);
+
 // Device status word of each translation unit (read-and-clear).
 int segreduce_status(int *out);
 int gather_status(int *out);

@@ -1436,6 +1436,223 @@ int plan_build(cgnn_plan *p, const int32_t *const rowptr[2], const int32_t *cons
     return CGNN_OK;
 }
 
+// ---------------------------------------------------------------------------------------
+// Plan construction on the device (see cgnn_plan.h): the decisions of plan_build, taken by one CTA.
+// ---------------------------------------------------------------------------------------
+constexpr int PLAN_CTA = 1024;
+constexpr int PLAN_HIST_CAP = 4096;
+
+__global__ void __launch_bounds__(PLAN_CTA) plan_stats_kernel(const int32_t *rowptr, const int32_t *last_row_dev,
+                                                              int64_t nnz, int split_request, int32_t *header) {
+    __shared__ int hist[PLAN_HIST_CAP + 1];
+    __shared__ int s_max, s_split, s_short, s_long, s_items, s_short_entries;
+    const int rows = *last_row_dev + 1;
+    for (int i = threadIdx.x; i <= PLAN_HIST_CAP; i += PLAN_CTA) hist[i] = 0;
+    if (threadIdx.x == 0) s_max = s_short = s_long = s_items = s_short_entries = 0;
+    __syncthreads();
+    int longest = 0;
+    for (int r = threadIdx.x; r < rows; r += PLAN_CTA) {
+        const int d = rowptr[r + 1] - rowptr[r];
+        atomicAdd(&hist[min(d, PLAN_HIST_CAP)], 1);
+        longest = max(longest, d);
+    }
+    atomicMax(&s_max, longest);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // smallest length whose cumulative count reaches ceil(q * rows): the host path's percentile
+        const int want50 = (rows + 1) / 2, want99 = (int)((99ll * rows + 99) / 100);
+        int seen = 0, p50 = -1, p99 = -1;
+        for (int d = 0; d <= PLAN_HIST_CAP && p99 < 0; ++d) {
+            seen += hist[d];
+            if (p50 < 0 && seen >= want50) p50 = d;
+            if (seen >= want99) p99 = d;
+        }
+        header[PH_P50] = max(p50, 0);
+        header[PH_P99] = max(p99, 0);
+        s_split = split_request > 0 ? split_request : ((nnz > 64ll * rows || p99 > 512) ? 128 : 64);
+    }
+    __syncthreads();
+    const int split = s_split;
+    int n_short = 0, n_long = 0, n_items = 0, short_entries = 0;
+    for (int r = threadIdx.x; r < rows; r += PLAN_CTA) {
+        const int d = rowptr[r + 1] - rowptr[r];
+        if (d > split) {
+            ++n_long;
+            n_items += (d + split - 1) / split;
+        } else {
+            n_short += d > 0;
+            short_entries += d;
+        }
+    }
+    atomicAdd(&s_short, n_short);
+    atomicAdd(&s_long, n_long);
+    atomicAdd(&s_items, n_items);
+    atomicAdd(&s_short_entries, short_entries);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int compact = rows >= 1024 && 2ll * s_short < rows;
+        header[PH_ROWS] = rows;
+        header[PH_SPLIT] = split;
+        header[PH_COMPACT] = compact;
+        header[PH_IDENTITY] = !compact && s_long == 0;
+        header[PH_DIRECT] = compact ? s_short : rows - s_long;
+        header[PH_LONG] = s_long;
+        header[PH_ITEMS] = s_items;
+        header[PH_MAX] = s_max;
+        header[PH_SHORT_ENTRIES] = s_short_entries;
+        header[PH_VALID] = 1;
+    }
+}
+
+// One CTA: thread t owns a contiguous slice of the rows; five block-wide prefix sums place its listed
+// rows, long rows, chunks and entries; a second walk over the slice writes the lists.
+__global__ void __launch_bounds__(PLAN_CTA) plan_fill_kernel(const int32_t *rowptr, int rows, int split, int compact,
+                                                             int identity, int32_t *uptr, int32_t *urow, int4 *longs,
+                                                             int32_t *dst) {
+    __shared__ int scan[5][PLAN_CTA + 1];
+    const int per = (rows + PLAN_CTA - 1) / PLAN_CTA;
+    const int r0 = min(rows, (int)threadIdx.x * per), r1 = min(rows, r0 + per);
+    int mine[5] = {0, 0, 0, 0, 0};  // listed rows, their entries, long rows, their entries, chunks
+    for (int r = r0; r < r1; ++r) {
+        const int d = rowptr[r + 1] - rowptr[r];
+        if (d > split) {
+            ++mine[2];
+            mine[3] += d;
+            mine[4] += (d + split - 1) / split;
+        } else if (!(compact && d == 0)) {
+            ++mine[0];
+            mine[1] += d;
+        }
+    }
+#pragma unroll
+    for (int q = 0; q < 5; ++q) scan[q][threadIdx.x + 1] = mine[q];
+    if (threadIdx.x == 0)
+        for (int q = 0; q < 5; ++q) scan[q][0] = 0;
+    __syncthreads();
+    // inclusive prefix sums in place (Hillis-Steele over PLAN_CTA + 1 slots, slot 0 stays 0)
+    for (int step = 1; step <= PLAN_CTA; step <<= 1) {
+        int add[5];
+        const int i = threadIdx.x + 1;
+#pragma unroll
+        for (int q = 0; q < 5; ++q) add[q] = i >= step ? scan[q][i - step] : 0;
+        __syncthreads();
+#pragma unroll
+        for (int q = 0; q < 5; ++q) scan[q][i] += add[q];
+        __syncthreads();
+    }
+    int listed = scan[0][threadIdx.x], pos = scan[1][threadIdx.x], lrow = scan[2][threadIdx.x];
+    const int short_total = scan[1][PLAN_CTA];
+    int lpos = short_total + scan[3][threadIdx.x], item = scan[4][threadIdx.x];
+    for (int r = r0; r < r1; ++r) {
+        const int d = rowptr[r + 1] - rowptr[r];
+        if (d > split) {
+            const int chunks = (d + split - 1) / split;
+            longs[lrow++] = make_int4(r, item, chunks, lpos);
+            dst[r] = lpos;
+            item += chunks;
+            lpos += d;
+        } else if (!(compact && d == 0)) {
+            uptr[listed] = pos;
+            if (!identity) urow[listed] = r;
+            ++listed;
+            dst[r] = pos;
+            pos += d;
+        } else {
+            dst[r] = 0;
+        }
+    }
+    if (threadIdx.x == PLAN_CTA - 1) uptr[scan[0][PLAN_CTA]] = short_total;
+}
+
+// One thread per chunk: find its long row (the last one whose first chunk is not beyond it).
+__global__ void plan_items_kernel(const int32_t *rowptr, const int4 *longs, int n_long, int4 *items, int n_items,
+                                  int split) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_items; i += blockDim.x * gridDim.x) {
+        int lo = 0, hi = n_long - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (longs[mid].y <= i) lo = mid;
+            else hi = mid - 1;
+        }
+        const int4 lr = longs[lo];
+        const int d = rowptr[lr.x + 1] - rowptr[lr.x];
+        const int o = (i - lr.y) * split;
+        items[i] = make_int4(lo, lr.w + o, lr.w + min(o + split, d), 0);
+    }
+}
+
+int plan_stats_on_device(const int32_t *rowptr, const int32_t *last_row_dev, int64_t nnz, int split,
+                         int32_t *header_dev, cudaStream_t stream) {
+    CGNN_CUDA(cudaMemsetAsync(header_dev, 0, sizeof(int32_t) * PLAN_HEADER_WORDS, stream));
+    plan_stats_kernel<<<1, PLAN_CTA, 0, stream>>>(rowptr, last_row_dev, nnz, split, header_dev);
+    CGNN_LAUNCH_CHECK();
+    return CGNN_OK;
+}
+
+int plan_fill_on_device(cgnn_plan *p, const int32_t *rowptr, const int32_t *col, const int32_t *h,
+                        cudaStream_t stream) {
+    CGNN_REQUIRE(h[PH_VALID] == 1 && h[PH_ROWS] == p->rows, "plan: the device-side row statistics do not match");
+    const int64_t rows = p->rows, total = p->nnz[0];
+    p->total = total;
+    p->split = h[PH_SPLIT];
+    p->compact = h[PH_COMPACT];
+    p->n_direct = h[PH_DIRECT];
+    p->n_long = h[PH_LONG];
+    p->n_items = h[PH_ITEMS];
+    p->degree_p50 = h[PH_P50];
+    p->degree_p99 = h[PH_P99];
+    p->degree_max = h[PH_MAX];
+    p->source_rows[0] = total;  // the columns of an index plan are the positions 0 .. nnz-1
+    p->source_rows[1] = 0;
+    const bool identity = h[PH_IDENTITY] != 0;
+    auto span = [](size_t bytes) { return align_up(std::max<size_t>(bytes, 16), 256); };
+    const size_t o_uptr = 0;
+    const size_t o_urow = o_uptr + span(((size_t)p->n_direct + 1) * 4);
+    const size_t o_items = o_urow + span(identity ? 0 : (size_t)p->n_direct * 4);
+    const size_t o_longs = o_items + span((size_t)p->n_items * 16);
+    const size_t o_dst = o_longs + span((size_t)p->n_long * 16);
+    const size_t o_maxsrc = o_dst + span((size_t)rows * 4);
+    const size_t o_entries = o_maxsrc + span(2 * 4);
+    const size_t bytes = o_entries + span((size_t)total * 4);
+    p->home = stream;
+    p->pooled = pool_alloc(&p->block, bytes, stream) == cudaSuccess;
+    if (!p->pooled) {
+        cudaGetLastError();
+        if (cudaMalloc(&p->block, bytes) != cudaSuccess) {
+            cudaGetLastError();
+            p->block = nullptr;
+            set_error("plan: device allocation of %zu bytes failed", bytes);
+            return CGNN_ERR_CUDA;
+        }
+    }
+    char *base = reinterpret_cast<char *>(p->block);
+    p->uptr = reinterpret_cast<int32_t *>(base + o_uptr);
+    p->urow = identity ? nullptr : reinterpret_cast<int32_t *>(base + o_urow);
+    p->items = reinterpret_cast<int4 *>(base + o_items);
+    p->longs = reinterpret_cast<int4 *>(base + o_longs);
+    p->entries = reinterpret_cast<int32_t *>(base + o_entries);
+    p->vperm = nullptr;
+    int32_t *dst = reinterpret_cast<int32_t *>(base + o_dst);
+    int32_t *max_source = reinterpret_cast<int32_t *>(base + o_maxsrc);
+    CGNN_CUDA(cudaMemsetAsync(max_source, 0xff, 2 * sizeof(int32_t), stream));
+    plan_fill_kernel<<<1, PLAN_CTA, 0, stream>>>(rowptr, (int)rows, p->split, p->compact, identity ? 1 : 0, p->uptr,
+                                                 reinterpret_cast<int32_t *>(base + o_urow), p->longs, dst);
+    CGNN_LAUNCH_CHECK();
+    if (p->n_items > 0) {
+        const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(p->n_items, 256), 148 * 8);
+        plan_items_kernel<<<blocks, 256, 0, stream>>>(rowptr, p->longs, (int)p->n_long, p->items, (int)p->n_items,
+                                                      p->split);
+        CGNN_LAUNCH_CHECK();
+    }
+    if (total > 0) {
+        const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(rows, 8), 148 * 16));
+        scatter_entries_kernel<<<blocks, 256, 0, stream>>>(rowptr, col, dst, nullptr, rows, 0, 0, p->entries, nullptr,
+                                                           max_source);
+        CGNN_LAUNCH_CHECK();
+    }
+    return CGNN_OK;
+}
+
 template <typename InT>
 __global__ void convert_index_kernel(const InT *in, int32_t *out, int64_t n, int64_t limit) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;

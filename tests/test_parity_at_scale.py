@@ -149,6 +149,22 @@ def test_cluster_workload_shape_600k_nodes():
     assert_close_rel(db.cpu().numpy(), ref_db, what="bias gradient")
     assert rt.device_status() == 0
 
+    # the reference's own CUDA operators on the same tensors, when they are built (second checker)
+    ref_cuda = oracle.reference_cuda_module()
+    if ref_cuda is not None:
+        c_ids, c_counts, c_active = ref_cuda.cluster_assign(dx, dp, bits, ref_cuda.cluster_workspace(dx, bits))
+        c_ids = c_ids.cpu().numpy()
+        pairs = np.unique(np.stack([rids[clear], c_ids[clear]], axis=1), axis=0)
+        assert np.all(np.diff(pairs[:, 0]) > 0) and np.all(np.diff(pairs[:, 1]) > 0)
+        if ambiguous == 0:
+            assert c_active == active and np.array_equal(c_ids, rids)
+            np.testing.assert_array_equal(c_counts.cpu().numpy(), rcounts)
+        assert_close_rel(reps.cpu().numpy(), ref_cuda.cluster_mean(dx, ids, counts).cpu().numpy(), what="mean vs reference CUDA")
+        np.testing.assert_array_equal(y.cpu().numpy(), ref_cuda.cluster_reconstruct(cu(table), ids, cu(bias), True).cpu().numpy())
+        assert_close_rel(exact.cpu().numpy(),
+                         ref_cuda.cluster_reconstruct_backward(dgo, ids, y, groups, True).cpu().numpy(),
+                         what="reconstruct backward vs reference CUDA")
+
 
 def test_gcn_epoch_on_the_propagation_graph(web_graph):
     """One training epoch of the config-5 model (F=64 input, hidden 128, 47 classes, H=16) against
