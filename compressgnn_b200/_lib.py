@@ -55,6 +55,8 @@ SIGNATURES = {
                                             _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
     "cgnn_cluster_reconstruct": (_c_int, [_c_int, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr,
                                           _c_int, _c_ptr, _c_ptr]),
+    "cgnn_cluster_reconstruct_dropout": (_c_int, [_c_int, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr,
+                                                  ctypes.c_double, ctypes.c_uint64, _c_ptr, _c_ptr]),
     "cgnn_cluster_reconstruct_backward": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_int,
                                                    _c_ptr, _c_ptr, _c_ptr, _c_size, _c_ptr]),
 }

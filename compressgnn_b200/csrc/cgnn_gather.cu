@@ -39,7 +39,42 @@ struct ExpandArgs {
     int relu;
     T *out;
     int64_t n, width, groups;
+    // optional dropout after the activation: an element is dropped when its 32-bit random word is below
+    // drop_threshold, the survivors are multiplied by keep_scale = 1 / (1 - p); 0 = no dropout
+    uint32_t drop_threshold = 0;
+    float keep_scale = 1.f;
+    uint64_t seed = 0;
 };
+
+// Philox4x32 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC 2011) with 7
+// rounds: four 32-bit words for the counter (element-vector index, 0) under the key `seed`.  Counter
+// based, so the words of an element do not depend on which thread produces them.
+__device__ __forceinline__ uint4 philox4x32_7(uint64_t counter, uint64_t seed) {
+    uint32_t c0 = (uint32_t)counter, c1 = (uint32_t)(counter >> 32), c2 = 0x243F6A88u, c3 = 0x85A308D3u;
+    uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+    for (int round = 0; round < 7; ++round) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        c0 = hi1 ^ c1 ^ k0;
+        c1 = lo1;
+        c2 = hi0 ^ c3 ^ k1;
+        c3 = lo0;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    return make_uint4(c0, c1, c2, c3);
+}
+
+// Dropout of the VW values of the vector that starts at element `first` of the output (VW <= 4).
+template <typename T, int VW>
+__device__ __forceinline__ void drop_vector(Vec<T, VW> &y, int64_t first, uint32_t threshold, float keep_scale,
+                                            uint64_t seed) {
+    const uint4 r = philox4x32_7((uint64_t)first, seed);
+    const uint32_t word[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int k = 0; k < VW; ++k) y.v[k] = word[k] < threshold ? T(0) : y.v[k] * (T)keep_scale;
+}
 
 // A group of LPR lanes expands LPR consecutive node rows per step: lane l reads index[r0 + l]
 // (one coalesced load), the indices are broadcast by shuffle, and U table rows are in flight
@@ -91,6 +126,8 @@ __global__ void __launch_bounds__(256) expand_kernel(const ExpandArgs<T> a) {
                             if (a.div_counts) v = v / divisor[u];
                             y.v[k] = (a.relu && v < T(0)) ? T(0) : v;
                         }
+                        if (a.drop_threshold)
+                            drop_vector<T, VW>(y, (r0 + j + u) * a.width + c * VW, a.drop_threshold, a.keep_scale, a.seed);
                         vec_store_cs<T, VW>(a.out + (r0 + j + u) * a.width + c * VW, y);
                     }
                 }
@@ -103,7 +140,7 @@ __global__ void __launch_bounds__(256) expand_kernel(const ExpandArgs<T> a) {
 // at benchmark widths): a warp expands 32 node rows per step, each lane owns VPL vectors of a row,
 // and bias / ReLU are compile-time switches, so that the per-row work is one index shuffle, one
 // row-base multiply, VPL loads, the epilogue and VPL streaming stores.
-template <typename T, int VW, int VPL, int U, bool BIAS, bool RELU>
+template <typename T, int VW, int VPL, int U, bool BIAS, bool RELU, bool DROP>
 __global__ void __launch_bounds__(256, CGNN_EXPAND_WIDE_MINBLOCKS) expand_wide_kernel(const ExpandArgs<T> a) {
     using V = Vec<T, VW>;
     constexpr unsigned FULL = 0xffffffffu;
@@ -158,6 +195,8 @@ __global__ void __launch_bounds__(256, CGNN_EXPAND_WIDE_MINBLOCKS) expand_wide_k
                                     if (BIAS) v += b[p].v[k];
                                     y.v[k] = (RELU && v < T(0)) ? T(0) : v;
                                 }
+                                if constexpr (DROP)
+                                    drop_vector<T, VW>(y, (orow - a.out) + col[p], a.drop_threshold, a.keep_scale, a.seed);
                                 vec_store_cs<T, VW>(orow + col[p], y);
                             }
                         }
@@ -174,14 +213,19 @@ static int launch_expand_wide(const ExpandArgs<T> &a, cudaStream_t stream) {
     constexpr int U = 8 / VPL;  // 8 vectors in flight per lane
     const int64_t blocks = std::min<int64_t>(ceil_div(a.n, 32 * 8), 148 * 32);
     const bool bias = a.bias != nullptr, relu = a.relu != 0;
-    if (bias && relu)
-        expand_wide_kernel<T, VW, VPL, U, true, true><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    if (a.drop_threshold) {  // the hidden layers of the model: always with ReLU, with or without bias
+        if (bias)
+            expand_wide_kernel<T, VW, VPL, U, true, true, true><<<(unsigned)blocks, 256, 0, stream>>>(a);
+        else
+            expand_wide_kernel<T, VW, VPL, U, false, true, true><<<(unsigned)blocks, 256, 0, stream>>>(a);
+    } else if (bias && relu)
+        expand_wide_kernel<T, VW, VPL, U, true, true, false><<<(unsigned)blocks, 256, 0, stream>>>(a);
     else if (bias)
-        expand_wide_kernel<T, VW, VPL, U, true, false><<<(unsigned)blocks, 256, 0, stream>>>(a);
+        expand_wide_kernel<T, VW, VPL, U, true, false, false><<<(unsigned)blocks, 256, 0, stream>>>(a);
     else if (relu)
-        expand_wide_kernel<T, VW, VPL, U, false, true><<<(unsigned)blocks, 256, 0, stream>>>(a);
+        expand_wide_kernel<T, VW, VPL, U, false, true, false><<<(unsigned)blocks, 256, 0, stream>>>(a);
     else
-        expand_wide_kernel<T, VW, VPL, U, false, false><<<(unsigned)blocks, 256, 0, stream>>>(a);
+        expand_wide_kernel<T, VW, VPL, U, false, false, false><<<(unsigned)blocks, 256, 0, stream>>>(a);
     CGNN_LAUNCH_CHECK();
     return CGNN_OK;
 }
@@ -236,19 +280,25 @@ static int expand_typed(const ExpandArgs<T> &a, cudaStream_t stream) {
 
 static int expand(int dtype, int64_t n, int64_t width, int64_t groups, const void *table,
                   const int64_t *index, const void *bias, const int32_t *div_counts, int relu,
-                  void *out, cudaStream_t stream) {
+                  void *out, cudaStream_t stream, double drop_p = 0.0, uint64_t seed = 0) {
     CGNN_REQUIRE(dtype == CGNN_F32 || dtype == CGNN_F64, "gather: unknown dtype %d", dtype);
     CGNN_REQUIRE(n >= 0 && width >= 0 && groups >= 0, "gather: negative size");
     if (n > 0 && width > 0)
         CGNN_REQUIRE(table != nullptr && index != nullptr && out != nullptr,
                      "gather: null pointer");
+    uint32_t threshold = 0;
+    float keep_scale = 1.f;
+    if (drop_p > 0.0) {
+        threshold = (uint32_t)std::min<double>(drop_p * 4294967296.0, 4294967295.0);
+        keep_scale = (float)(1.0 / (1.0 - drop_p));
+    }
     if (dtype == CGNN_F32) {
         ExpandArgs<float> a{(const float *)table, index, (const float *)bias, div_counts, relu,
-                            (float *)out, n, width, groups};
+                            (float *)out, n, width, groups, threshold, keep_scale, seed};
         return expand_typed<float>(a, stream);
     }
     ExpandArgs<double> a{(const double *)table, index, (const double *)bias, div_counts, relu,
-                         (double *)out, n, width, groups};
+                         (double *)out, n, width, groups, threshold, keep_scale, seed};
     return expand_typed<double>(a, stream);
 }
 
@@ -285,6 +335,13 @@ int cgnn_cluster_reconstruct(int dtype, int64_t n, int64_t width, int64_t groups
                              void *out, cgnn_stream_t stream) {
     return expand(dtype, n, width, groups, reps, index, bias, nullptr, relu, out,
                   (cudaStream_t)stream);
+}
+
+int cgnn_cluster_reconstruct_dropout(int dtype, int64_t n, int64_t width, int64_t groups,
+                                     const void *reps, const int64_t *index, const void *bias,
+                                     double drop_p, uint64_t seed, void *out, cgnn_stream_t stream) {
+    CGNN_REQUIRE(drop_p >= 0.0 && drop_p < 1.0, "reconstruct_dropout: the drop probability must lie in [0, 1)");
+    return expand(dtype, n, width, groups, reps, index, bias, nullptr, 1, out, (cudaStream_t)stream, drop_p, seed);
 }
 
 }  // extern "C"

@@ -128,7 +128,7 @@ class ShardedGNNLayer(torch.nn.Module):
     def reset_cache(self):
         self.cluster.reset_cache()
 
-    def forward(self, x_local, edge_index, edge_weight=None, vertex_cnt=0, rule_cnt=0):
+    def forward(self, x_local, edge_index, edge_weight=None, vertex_cnt=0, rule_cnt=0, dropout=0.0):
         p = self.P(x=x_local, edge_index=edge_index, edge_weight=edge_weight, vertex_cnt=vertex_cnt,
                    rule_cnt=rule_cnt)
         reps_local, index = self.cluster(p)
@@ -137,8 +137,10 @@ class ShardedGNNLayer(torch.nn.Module):
         if self.shard_output:
             begin, end = column_range(self.lin.out_features, self.rank, self.world)
             weight, bias = weight[begin:end], bias[begin:end]
-        return self.reconstruct(torch.nn.functional.linear(reps, weight, None), index, bias=bias,
-                                activation=self.activation)
+        fused = dropout if self.activation == "relu" else 0.0
+        out = self.reconstruct(torch.nn.functional.linear(reps, weight, None), index, bias=bias,
+                               activation=self.activation, dropout=fused)
+        return torch.nn.functional.dropout(out, p=dropout) if dropout and not fused else out
 
 
 class ShardedGCN(torch.nn.Module):
@@ -171,9 +173,8 @@ class ShardedGCN(torch.nn.Module):
         last = len(self.layers) - 1
         x = x_local
         for i, layer in enumerate(self.layers):
-            x = layer(x, edge_index, edge_weight, vertex_cnt, rule_cnt)
-            if i != last and dropout:
-                x = torch.nn.functional.dropout(x, p=self.dropout, training=self.training)
+            p = self.dropout if (i != last and dropout and self.training) else 0.0
+            x = layer(x, edge_index, edge_weight, vertex_cnt, rule_cnt, dropout=p)
         return torch.nn.functional.log_softmax(x, dim=1)
 
     def consolidate_parameters(self):

@@ -31,14 +31,20 @@ class GNNLayer(torch.nn.Module):
     def reset_cache(self):
         self.cluster.reset_cache()
 
-    def forward(self, x: Tensor, edge_index, edge_weight=None, vertex_cnt: int = 0, rule_cnt: int = 0) -> Tensor:
+    def forward(self, x: Tensor, edge_index, edge_weight=None, vertex_cnt: int = 0, rule_cnt: int = 0,
+                dropout: float = 0.0) -> Tensor:
+        """``dropout``: probability of the dropout the model applies to this layer's (ReLU) output; with the
+        transformation path it runs inside the reconstruct kernel."""
         x = self.P(x=x, edge_index=edge_index, edge_weight=edge_weight, vertex_cnt=vertex_cnt, rule_cnt=rule_cnt)
         if self.use_transformation:
             reps, index = self.cluster(x)
-            return self.reconstruct(F.linear(reps, self.lin.weight, None), index, bias=self.lin.bias,
-                                    activation=self.activation)
+            fused = dropout if self.activation == "relu" else 0.0
+            x = self.reconstruct(F.linear(reps, self.lin.weight, None), index, bias=self.lin.bias,
+                                 activation=self.activation, dropout=fused)
+            return F.dropout(x, p=dropout) if dropout and not fused else x
         x = self.lin(x)
-        return x.relu() if self.activation == "relu" else x
+        x = x.relu() if self.activation == "relu" else x
+        return F.dropout(x, p=dropout) if dropout else x
 
 
 class GCN(torch.nn.Module):
@@ -63,9 +69,10 @@ class GCN(torch.nn.Module):
     def _stack(self, x, edge_index, edge_weight, vertex_cnt, rule_cnt, dropout):
         last = len(self.layers) - 1
         for i, layer in enumerate(self.layers):
-            x = layer(x=x, edge_index=edge_index, edge_weight=edge_weight, vertex_cnt=vertex_cnt, rule_cnt=rule_cnt)
-            if i != last and dropout:  # the hidden layers' ReLU is part of the layer (fused reconstruct)
-                x = F.dropout(x, p=self.dropout, training=self.training)
+            # the hidden layers' ReLU and dropout are part of the layer (fused into the reconstruct kernel)
+            p = self.dropout if (i != last and dropout and self.training) else 0.0
+            x = layer(x=x, edge_index=edge_index, edge_weight=edge_weight, vertex_cnt=vertex_cnt, rule_cnt=rule_cnt,
+                      dropout=p)
         return F.log_softmax(x, dim=1)
 
     def forward(self, x: Tensor, edge_index, edge_weight=None, vertex_cnt: int = 0, rule_cnt: int = 0) -> Tensor:

@@ -493,8 +493,10 @@ def cluster_mean_backward(grad, index, count):
     return out
 
 
-def cluster_reconstruct(reps, index, bias, relu):
-    """``out[r] = act(reps[index[r]] + bias)``; ``bias`` may be None."""
+def cluster_reconstruct(reps, index, bias, relu, dropout_p=0.0, seed=0):
+    """``out[r] = act(reps[index[r]] + bias)``; ``bias`` may be None.  With ``dropout_p > 0`` (ReLU only)
+    the same pass also drops elements with that probability and scales the survivors by
+    ``1 / (1 - dropout_p)``; the mask is a function of ``(seed, element position)``."""
     _check_float(reps)
     _check_index(index, reps.device)
     if bias is not None:
@@ -504,11 +506,19 @@ def cluster_reconstruct(reps, index, bias, relu):
     out = torch.empty((index.numel(), reps.size(1)), dtype=reps.dtype, device=reps.device)
     if out.numel() == 0:
         return out
+    dropout_p = float(dropout_p)
+    _require(0.0 <= dropout_p < 1.0, "dropout probability must lie in [0, 1)")
+    _require(dropout_p == 0.0 or relu, "the fused dropout follows a ReLU (the backward reads its mask off the zeros)")
     with torch.cuda.device(reps.device):
-        check(lib().cgnn_cluster_reconstruct(_dtype_code(reps), index.numel(), reps.size(1),
-                                             reps.size(0), _ptr(reps), _ptr(index), _ptr(bias),
-                                             1 if relu else 0, _ptr(out),
-                                             _stream_ptr(reps.device)))
+        if dropout_p > 0.0:
+            check(lib().cgnn_cluster_reconstruct_dropout(
+                _dtype_code(reps), index.numel(), reps.size(1), reps.size(0), _ptr(reps), _ptr(index), _ptr(bias),
+                dropout_p, int(seed) & (2**64 - 1), _ptr(out), _stream_ptr(reps.device)))
+        else:
+            check(lib().cgnn_cluster_reconstruct(_dtype_code(reps), index.numel(), reps.size(1),
+                                                 reps.size(0), _ptr(reps), _ptr(index), _ptr(bias),
+                                                 1 if relu else 0, _ptr(out),
+                                                 _stream_ptr(reps.device)))
     return out
 
 

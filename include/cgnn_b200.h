@@ -229,6 +229,19 @@ int cgnn_cluster_reconstruct(int dtype, int64_t n, int64_t width, int64_t groups
                              const void *reps, const int64_t *index, const void *bias,
                              int relu, void *out, cgnn_stream_t stream);
 
+/* The hidden-layer epilogue of the reference's model in one pass:
+ *   out[r,:] = dropout_p(relu(reps[index[r],:] + bias))
+ * (ref: model/compressgnn/gcn.py:54-61 applies F.relu and F.dropout to the reconstructed [N,F]
+ * matrix as two further elementwise passes.)  An element is dropped with probability drop_p, the
+ * others are scaled by 1/(1-drop_p); the random words are Philox4x32 outputs counted by the
+ * element's position under the key `seed`, so the mask depends on (seed, position) only.  The
+ * backward pass needs no mask tensor: with ReLU in front, a dropped element and a clamped one both
+ * read 0 in `out`, which cgnn_cluster_reconstruct_backward's exact-mask mode (relu = 1) turns into
+ * a zero gradient; the caller multiplies the result by 1/(1-drop_p). */
+int cgnn_cluster_reconstruct_dropout(int dtype, int64_t n, int64_t width, int64_t groups,
+                                     const void *reps, const int64_t *index, const void *bias,
+                                     double drop_p, uint64_t seed, void *out, cgnn_stream_t stream);
+
 /* d_reps[g,:] = sum_{index[r]==g} (relu && output[r,:] <= 0 ? 0 : grad[r,:]);
  * relu: 0 = no mask; 1 = mask read per node row from `output` (the reference's semantics for
  * any `output`); 2 = `output` is known to be the forward result of cgnn_cluster_reconstruct,

@@ -261,6 +261,74 @@ def test_gcn_with_both_compressions_trains_one_step():
     assert model.layers[0].cluster.refresh_count == 1  # reused at epoch 1
 
 
+@pytest.mark.parametrize("width", [128, 256, 24, 6])
+def test_reconstruct_with_fused_dropout(width):
+    """The hidden-layer epilogue in one pass: dropout_p(relu(reps[index] + bias)).  Every output element is
+    either 0 or the plain result divided by (1 - p); the mask depends on the seed only; the backward equals
+    autograd through the same mask written out in plain torch."""
+    from compressgnn_b200 import runtime as rt
+    from compressgnn_b200.layer import Compressgnn_Reconstruct
+    gen = torch.Generator(device="cuda").manual_seed(width)
+    n, groups, p = 20000, 300, 0.3
+    reps = torch.randn(groups, width, device="cuda", generator=gen)
+    bias = torch.randn(width, device="cuda", generator=gen)
+    index = torch.randint(1, groups, (n,), device="cuda", generator=gen)
+    plain = rt.cluster_reconstruct(reps, index, bias, True)
+    fused = rt.cluster_reconstruct(reps, index, bias, True, dropout_p=p, seed=1234)
+    kept = fused != 0
+    torch.testing.assert_close(fused[kept], plain[kept] / (1 - p), rtol=1e-6, atol=0)
+    positive = plain > 0
+    rate = 1.0 - (kept & positive).sum().item() / positive.sum().item()
+    assert abs(rate - p) < 0.01, rate
+    assert torch.equal(fused, rt.cluster_reconstruct(reps, index, bias, True, dropout_p=p, seed=1234))
+    other = rt.cluster_reconstruct(reps, index, bias, True, dropout_p=p, seed=1235)
+    assert (other != fused).float().mean().item() > 0.1
+    # neighbouring elements are dropped independently: the drop rate of each column is close to p as well
+    # (columns whose bias leaves fewer than 2000 positive elements say little and are left out)
+    enough = positive.sum(0) >= 2000
+    col_rate = 1.0 - (kept & positive).sum(0).float() / positive.sum(0).float().clamp_min(1)
+    assert enough.sum().item() >= width // 2
+    assert (col_rate - p).abs()[enough].max().item() < 0.05
+    with pytest.raises(RuntimeError):
+        rt.cluster_reconstruct(reps, index, bias, False, dropout_p=p)
+    with pytest.raises(ValueError):
+        Compressgnn_Reconstruct()(reps, index, bias=bias, activation=None, dropout=p)
+    # autograd: the module against plain torch with the realised mask
+    torch.manual_seed(7)
+    src = reps.clone().requires_grad_()
+    b = bias.clone().requires_grad_()
+    out = Compressgnn_Reconstruct()(src, index, bias=b, activation="relu", dropout=p)
+    go = torch.randn(n, width, device="cuda", generator=gen)
+    g_src, g_b = torch.autograd.grad(out, (src, b), go)
+    src2, b2 = reps.clone().requires_grad_(), bias.clone().requires_grad_()
+    ref = (src2.index_select(0, index) + b2).relu() * (out != 0) / (1 - p)
+    torch.testing.assert_close(out, ref, rtol=1e-6, atol=1e-6)
+    r_src, r_b = torch.autograd.grad(ref, (src2, b2), go)
+    torch.testing.assert_close(g_src, r_src, rtol=1e-4, atol=1e-4)
+    # 20000 terms of magnitude ~1 per column, summed in two different orders in fp32; one wrongly masked
+    # element would move a column by ~1
+    torch.testing.assert_close(g_b, r_b, rtol=1e-4, atol=1e-2)
+
+
+def test_gcn_training_mode_uses_the_fused_dropout():
+    from compressgnn_b200.model import GCN
+    data = make_data(n=3000, width=32)
+    data.to("cuda")
+    torch.manual_seed(0)
+    model = GCN(32, 5, hidden_features=128, param_H=8, dropout=0.5, use_transformation=True, num_layers=2).cuda()
+    model.set_epoch(0)
+    hidden = []
+    hook = model.layers[0].register_forward_hook(lambda m, i, o: hidden.append(o.detach()))
+    out = model(data.x, data.edge_index)
+    out.logsumexp(1).sum().backward()
+    assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
+    model.eval()
+    model.inference(data.x, data.edge_index)
+    hook.remove()
+    train_zero, eval_zero = [(h == 0).float().mean().item() for h in hidden]
+    assert train_zero > eval_zero + 0.15   # half of the surviving (positive) activations are dropped in training
+
+
 def test_k_fold_propagation_with_cache():
     """KPUPropagate (ref: layer/KPUPropagate.py:25-37): K propagations in a row, and with
     cached=True the first result is kept and handed back detached whatever comes in later."""
