@@ -75,6 +75,31 @@ def test_projection_matches_the_oracle_bit_for_bit(rt):
         np.testing.assert_array_equal(ids.cpu().numpy(), rids)
 
 
+@pytest.mark.parametrize("bits", [4, 8, 12, 16, 20, 24, 28])
+@pytest.mark.parametrize("width", [16, 48, 128, 256])
+def test_tile_copy_projection_is_bit_exact(rt, bits, width):
+    """fp32, a width that is a multiple of 16 and a multiple of four planes take the kernel whose row
+    tiles arrive by TMA: every tile-boundary case against the oracle, and against the cp.async kernel
+    (reached through a feature matrix that starts 4 bytes off a 16-byte boundary)."""
+    rng = np.random.default_rng(31 * bits + width)
+    w = rng.standard_normal((width, bits)).astype(np.float32)
+    for n in (1, 255, 512, 513, 1024 + 77, 5000):
+        x = rng.standard_normal((n, width)).astype(np.float32)
+        want = oracle.project(x, w)
+        got = rt.project(cu(x), cu(w))
+        np.testing.assert_array_equal(got.cpu().numpy(), want)
+        ids, counts, active = assign(rt, cu(x), cu(w), bits)
+        rids, rcounts, ractive = oracle.cluster_assign(x, w)
+        assert active == ractive
+        np.testing.assert_array_equal(ids.cpu().numpy(), rids)
+        np.testing.assert_array_equal(counts.cpu().numpy(), rcounts)
+        shifted = torch.empty(n * width + 1, dtype=torch.float32, device="cuda")[1:].view(n, width)
+        shifted.copy_(cu(x))
+        assert shifted.data_ptr() % 16 == 4
+        assert torch.equal(rt.project(shifted, cu(w)), got)
+    rt.raise_on_device_status()
+
+
 def test_non_default_stream(rt):
     x = torch.randn(67, 33, device="cuda")
     w = torch.randn(33, 8, device="cuda")
