@@ -42,7 +42,7 @@ struct ExpandArgs {
     // optional dropout after the activation: an element is dropped when its 32-bit random word is below
     // drop_threshold, the survivors are multiplied by keep_scale = 1 / (1 - p); 0 = no dropout
     uint32_t drop_threshold = 0;
-    float keep_scale = 1.f;
+    T keep_scale = T(1);
     uint64_t seed = 0;
 };
 
@@ -68,12 +68,12 @@ __device__ __forceinline__ uint4 philox4x32_7(uint64_t counter, uint64_t seed) {
 
 // Dropout of the VW values of the vector that starts at element `first` of the output (VW <= 4).
 template <typename T, int VW>
-__device__ __forceinline__ void drop_vector(Vec<T, VW> &y, int64_t first, uint32_t threshold, float keep_scale,
+__device__ __forceinline__ void drop_vector(Vec<T, VW> &y, int64_t first, uint32_t threshold, T keep_scale,
                                             uint64_t seed) {
     const uint4 r = philox4x32_7((uint64_t)first, seed);
     const uint32_t word[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-    for (int k = 0; k < VW; ++k) y.v[k] = word[k] < threshold ? T(0) : y.v[k] * (T)keep_scale;
+    for (int k = 0; k < VW; ++k) y.v[k] = word[k] < threshold ? T(0) : y.v[k] * keep_scale;
 }
 
 // A group of LPR lanes expands LPR consecutive node rows per step: lane l reads index[r0 + l]
@@ -287,14 +287,14 @@ static int expand(int dtype, int64_t n, int64_t width, int64_t groups, const voi
         CGNN_REQUIRE(table != nullptr && index != nullptr && out != nullptr,
                      "gather: null pointer");
     uint32_t threshold = 0;
-    float keep_scale = 1.f;
+    double keep_scale = 1.0;
     if (drop_p > 0.0) {
         threshold = (uint32_t)std::min<double>(drop_p * 4294967296.0, 4294967295.0);
-        keep_scale = (float)(1.0 / (1.0 - drop_p));
+        keep_scale = 1.0 / (1.0 - drop_p);
     }
     if (dtype == CGNN_F32) {
         ExpandArgs<float> a{(const float *)table, index, (const float *)bias, div_counts, relu,
-                            (float *)out, n, width, groups, threshold, keep_scale, seed};
+                            (float *)out, n, width, groups, threshold, (float)keep_scale, seed};
         return expand_typed<float>(a, stream);
     }
     ExpandArgs<double> a{(const double *)table, index, (const double *)bias, div_counts, relu,

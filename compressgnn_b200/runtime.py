@@ -569,6 +569,32 @@ _STATUS_BITS = ((1, "an index outside its table was skipped"),
                 (4, "a CSR array held a negative or over-wide index"))
 
 
+def compress_csr_batch(vlist, elist, rounds=12, min_pair_frequency=16):
+    """Grammar compression of a CSR graph on the GPU (``cgnn_compress_csr_batch``): ``vlist`` /
+    ``elist`` are int64 CUDA tensors; returns ``(vlist int32, elist int32, vertices, rules)`` as CUDA
+    tensors with the arrays the host compressor of this package produces for the same input."""
+    _require(vlist.is_cuda and elist.is_cuda and vlist.device == elist.device, "compress_csr_batch needs CUDA tensors")
+    _require(vlist.dtype == torch.int64 and elist.dtype == torch.int64 and vlist.dim() == 1 and elist.dim() == 1 and
+             vlist.numel() >= 1, "compress_csr_batch needs one-dimensional int64 arrays")
+    vlist, elist = vlist.contiguous(), elist.contiguous()
+    device = vlist.device
+    handle = ctypes.c_void_p(0)
+    with torch.cuda.device(device):
+        stream = _stream_ptr(device)
+        check(lib().cgnn_compress_csr_batch(_ptr(vlist), _ptr(elist), vlist.numel() - 1, int(rounds),
+                                            int(min_pair_frequency), ctypes.byref(handle), stream))
+        try:
+            info = (ctypes.c_int64 * 3)()
+            check(lib().cgnn_compressed_info(handle, info))
+            n, rules, entries = int(info[0]), int(info[1]), int(info[2])
+            out_v = torch.empty(n + rules + 1, dtype=torch.int32, device=device)
+            out_e = torch.empty(entries, dtype=torch.int32, device=device)
+            check(lib().cgnn_compressed_copy(handle, _ptr(out_v), _ptr(out_e), stream))
+        finally:
+            lib().cgnn_compressed_destroy(handle)
+    return out_v, out_e, n, rules
+
+
 def raise_on_device_status():
     """``device_status()`` turned into an exception: raises RuntimeError naming the bits that were set."""
     status = device_status()

@@ -255,6 +255,31 @@ int cgnn_cluster_reconstruct_backward(const cgnn_plan *plan, int dtype, int64_t 
                                       void *d_reps, void *bias_grad, void *scratch,
                                       size_t scratch_bytes, cgnn_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Grammar compression of a CSR graph on the device (graph preparation, once per graph).
+ * ref: compress_csr_batch of the module compressgnn_batch_cuda, src/offline/bindings/batch_cuda.cpp:3-9,
+ * selected by loader/compression_backend.py:6-40.  The compressor behind that binding is an external
+ * project; the contract the reference's tests hold it to (tests/test_batch_compression.py:15-59) is:
+ * int32 arrays, rows n.. are rule bodies made of smaller symbols, every vertex row expands to its
+ * input row in order, and the CUDA result equals the CPU result.  Here the CPU result is this
+ * package's host compressor (rounds of digram substitution), and the device code reproduces its
+ * arrays exactly.
+ *
+ * vlist [n+1] and elist [vlist[n]] are DEVICE arrays of int64; values of elist must lie in [0, n)
+ * and n + vlist[n] must stay below 2^31 (CGNN_ERR_INVALID otherwise).  The call synchronises
+ * `stream` a few times per round and allocates its work arrays with cudaMalloc (about 60 bytes per
+ * input edge, released before it returns).  The result holds
+ *   vlist int32 [n + rules + 1], elist int32 [entries]   (device memory)
+ * cgnn_compressed_info: info = {n, rules, entries}.  cgnn_compressed_copy copies both arrays to
+ * host or device buffers of those sizes on `stream` (asynchronously: synchronise before reading). */
+typedef struct cgnn_compressed cgnn_compressed;
+int cgnn_compress_csr_batch(const int64_t *vlist, const int64_t *elist, int64_t n, int rounds,
+                            int min_frequency, cgnn_compressed **out, cgnn_stream_t stream);
+int cgnn_compressed_info(const cgnn_compressed *c, int64_t info[3]);
+int cgnn_compressed_copy(const cgnn_compressed *c, int32_t *vlist_out, int32_t *elist_out,
+                         cgnn_stream_t stream);
+void cgnn_compressed_destroy(cgnn_compressed *c);
+
 #ifdef __cplusplus
 }
 #endif

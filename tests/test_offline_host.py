@@ -83,9 +83,14 @@ def test_argument_errors():
     for bad in ['wrong', 'legacy', None]:
         with pytest.raises(ValueError):
             resolve_backend(bad)
-    assert resolve_backend('auto') == 'cpu'
-    with pytest.raises(RuntimeError):
-        resolve_backend('cuda')
+    assert resolve_backend('cpu') == 'cpu'
+    import torch
+    if torch.cuda.is_available():  # the device compressor is taken whenever a GPU is usable
+        assert resolve_backend('auto') == 'cuda' and resolve_backend('cuda') == 'cuda'
+    else:
+        assert resolve_backend('auto') == 'cpu'
+        with pytest.raises(RuntimeError):
+            resolve_backend('cuda')
 
 
 def test_partition_matches_the_reference_vectors(golden):
