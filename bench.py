@@ -80,10 +80,11 @@ def recorded_traffic(workload, width, world):
     return None, "no ncu capture of this workload"
 
 
-def build_graph(name):
+def build_graph(name, compression_backend="auto"):
     """Seeded copying-model graph -> CompressgnnData (self loops, symmetric normalisation,
     grammar compression, block partition).  Stands in for the public web graphs the reference's
-    scripts load; nothing of those datasets is used."""
+    scripts load; nothing of those datasets is used.  The host and the device compressor return the
+    same arrays, so the workload does not depend on `compression_backend`."""
     from compressgnn_b200 import offline as off
     from compressgnn_b200.loader import CompressgnnData
     w = WORKLOADS[name]
@@ -92,7 +93,8 @@ def build_graph(name):
                                            window=64, candidates=8, seed=w["seed"])
     mask = np.ones(n, dtype=bool)
     data = CompressgnnData(np.zeros((n, 1), np.float32), (vlist, elist), np.zeros(n, np.int64), mask, mask, mask,
-                           add_self_loop=True, normalize=True, graph_type="csr", **COMPRESS)
+                           add_self_loop=True, normalize=True, graph_type="csr",
+                           compression_backend=compression_backend, **COMPRESS)
     return data, int(elist.size)
 
 
@@ -897,7 +899,7 @@ def run_reference(args):
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     width_total, width = widths_for(args, world)
-    data, e_orig = build_graph(args.workload)
+    data, e_orig = build_graph(args.workload, compression_backend="cpu")  # nothing of this arm touches the GPU
     warmup = max(args.warmup, 3)
     # The CPU has no GPUs to scale over.  Strong scaling: it runs the whole job (all columns) whatever N
     # is.  Weak scaling (N blocks of columns): one block is timed and the step time multiplied by N.

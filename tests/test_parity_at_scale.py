@@ -32,6 +32,30 @@ def web_graph():
     return graph, blocks, e_orig
 
 
+def test_workload_graph_is_the_same_from_either_compressor(web_graph):
+    """The benchmark graph is compressed on the device when one is there: 3.4 M edges, rules nested in
+    rules over twelve rounds, hubs of 10^4 neighbours.  The host compressor must return the same arrays,
+    and so must everything downstream (filters, weights, transposition, block partition)."""
+    from compressgnn_b200 import offline as off
+    from compressgnn_b200.loader import compress_graph_csr
+    w = bench.WORKLOADS["propagation"]
+    v, e = off.generate_copy_graph(w["n"], alpha=2.1, x_min=w["x_min"], max_degree=10000, copy_prob=0.7, window=64,
+                                   candidates=8, seed=w["seed"])
+    v, e = off.add_self_loop_csr(v, e)
+    host = compress_graph_csr(v, e, bench.COMPRESS["min_pair_frequency"], backend="cpu")
+    device = compress_graph_csr(v, e, bench.COMPRESS["min_pair_frequency"], backend="cuda")
+    assert host[2:] == device[2:] and device[3] > 100000
+    np.testing.assert_array_equal(device[0], host[0])
+    np.testing.assert_array_equal(device[1], host[1])
+    _graph, blocks, _ = web_graph
+    data, _ = bench.build_graph("propagation", compression_backend="cpu")
+    g = data.edge_index
+    for k in ("v2v", "v2r", "r2v"):
+        for mine, theirs in zip(blocks[k], getattr(g, f"{k}_graph").csr()):
+            np.testing.assert_array_equal(mine, theirs.numpy())
+    assert len(blocks["r2r"]) == len(g.r2r_graph)
+
+
 @pytest.mark.parametrize("width", [256, 128, 16])
 def test_propagation_workload_against_reference_cpu(web_graph, width):
     from compressgnn_b200.layer import spmm as spmm_layer
