@@ -18,8 +18,9 @@ ranks); `e2e` goes through the public host-buffer front end with pinned host mat
 `roofline` is for the dominant kernel (the fused vertex pass of the forward); `cpu_baseline`
 is the reference's CPU spmm_func chain on this host's cores, and `parity_checked` compares the
 GPU's forward and backward results with that chain's on the same inputs.  `extra` carries short
-legs of the other two operator groups: the cluster / reconstruct operators at 2.45 M nodes and
-the 2-layer GCN epoch over four feature widths (sharded over the GPUs when N > 1).
+legs of the other operator groups: the cluster / reconstruct operators at 2.45 M nodes, the
+2-layer GCN epoch over four feature widths (sharded over the GPUs when N > 1), and the grammar
+compression of the workload's graph on the device beside the host compressor.
 """
 import argparse
 import json
@@ -495,6 +496,7 @@ def run_gpu(args):
     extra = {}
     if not args.no_extra and WORKLOADS[args.workload]["n"] < 2_000_000:
         if world == 1:
+            extra["compress"] = measure_compress(args.workload, 3, with_cpu=not args.no_cpu_baseline)
             extra["cluster"] = measure_cluster(args.cluster_nodes, max(3, min(args.steps, 10)), 3,
                                                with_cpu=not args.no_cpu_baseline)
         extra["gcn"] = measure_gcn(graph, e_orig, max(5, min(args.steps, 20)), 5, world, rank, device)
@@ -717,6 +719,53 @@ def measure_cluster(n, steps, warmup, with_cpu=True):
     return report
 
 
+def measure_compress(name, steps, with_cpu=True):
+    """Grammar compression of a workload's graph (self loops added) on the device, the two host arrays in
+    and the two host arrays out: host time around `compress_graph_csr(..., backend='cuda')`, the median of
+    `steps` calls after one warm-up call; the host compressor on the box's cores beside it, and whether the
+    two returned the same arrays."""
+    from compressgnn_b200 import offline as off
+    from compressgnn_b200.loader import compress_graph_csr
+    w = WORKLOADS[name]
+    vlist, elist = off.generate_copy_graph(w["n"], alpha=2.1, x_min=w["x_min"], max_degree=10000, copy_prob=0.7,
+                                           window=64, candidates=8, seed=w["seed"])
+    vlist, elist = off.add_self_loop_csr(vlist, elist)
+    frequency = COMPRESS["min_pair_frequency"]
+    device = compress_graph_csr(vlist, elist, frequency, backend="cuda")
+    times = []
+    for _ in range(max(steps, 1)):
+        t0 = time.perf_counter()
+        device = compress_graph_csr(vlist, elist, frequency, backend="cuda")
+        times.append(time.perf_counter() - t0)
+    sec = sorted(times)[len(times) // 2]
+    edges = int(elist.size)
+    report = {"metric": "compress_edges_per_s", "value": edges / sec / 1e6, "unit": "Medge/s", "ms_per_step": sec * 1e3,
+              "steps": len(times), "warmup": 1, "higher_is_better": True, "dtype": "int32", "data": "synthetic",
+              "config": {"workload": f"compress: digram-substitution grammar compression of the {name} graph, "
+                                     "host arrays in and out", "nodes": w["n"], "edges": edges,
+                         "entries_out": int(device[1].size), "rules": int(device[3]), "rounds": 12,
+                         "min_pair_frequency": frequency}}
+    if with_cpu:
+        cores = os.cpu_count() or 1
+        t0 = time.perf_counter()
+        host = compress_graph_csr(vlist, elist, frequency, backend="cpu", threads=cores)
+        host_sec = time.perf_counter() - t0
+        report["cpu_baseline"] = {"value": edges / host_sec / 1e6, "unit": "Medge/s", "cores": cores, "kind": "port",
+                                  "ms_per_step": host_sec * 1e3,
+                                  "sample": "the whole graph once, this package's host compressor (the reference's "
+                                            "compressor is an external project that its tree does not contain)"}
+        report["parity_checked"] = {"against": "host compressor", "arrays_equal": bool(
+            np.array_equal(device[0], host[0]) and np.array_equal(device[1], host[1]) and device[3] == host[3])}
+    return report
+
+
+def run_compress(args):
+    import torch
+    torch.cuda.set_device(0)
+    report = measure_compress(args.graph, min(args.steps, 5), with_cpu=not args.no_cpu_baseline)
+    print(json.dumps(dict(report, n_gpus=1, scaling="strong", vs_baseline=None, gpu_launches=None)))
+
+
 def run_cluster(args):
     import torch
     torch.cuda.set_device(0)
@@ -929,8 +978,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["cgnn", "reference"], default="cgnn")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cluster", "gcn"], default="propagation")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cluster", "gcn", "compress"], default="propagation")
     ap.add_argument("--cluster-nodes", type=int, default=2450000)
+    ap.add_argument("--graph", choices=sorted(WORKLOADS), default="propagation",
+                    help="graph of the compress workload")
     ap.add_argument("--width", type=int, default=0,
                     help="feature columns of a propagation workload (default: the workload's own)")
     ap.add_argument("--scaling", choices=["strong", "weak"], default="strong",
@@ -943,7 +994,9 @@ def main():
                     help="skip the informational leg that times the reference's own CUDA kernels")
     ap.add_argument("--no-extra", action="store_true", help="skip the cluster and GCN legs reported under `extra`")
     args = ap.parse_args()
-    if args.workload == "cluster":
+    if args.workload == "compress":
+        run_compress(args)
+    elif args.workload == "cluster":
         run_cluster(args)
     elif args.workload == "gcn":
         run_gcn(args)
