@@ -40,11 +40,31 @@ static inline unsigned blocks_for(int64_t count) {
 #define GRID_STRIDE(i, count) \
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < (count); i += (int64_t)blockDim.x * gridDim.x)
 
-// Device buffers of one compression, freed together.
+// Device buffers of one compression: the work arrays are carved out of one allocation (sized by a dry
+// pass of the same requests), the rule pairs of each round are allocated as the rounds find them.
 struct Arena {
     std::vector<void *> held;
+    char *block = nullptr;
+    size_t used = 0, capacity = 0;
+    bool sizing = true;
     ~Arena() {
         for (void *p : held) cudaFree(p);
+    }
+    template <typename T>
+    void carve(T **p, size_t count) {
+        const size_t bytes = align_up(std::max<size_t>(count, 1) * sizeof(T), 256);
+        *p = sizing ? nullptr : reinterpret_cast<T *>(block + used);
+        used += bytes;
+    }
+    cudaError_t commit() {  // end of the dry pass
+        capacity = used;
+        used = 0;
+        sizing = false;
+        void *raw = nullptr;
+        cudaError_t e = cudaMalloc(&raw, std::max<size_t>(capacity, 256));
+        if (e == cudaSuccess) held.push_back(raw);
+        block = reinterpret_cast<char *>(raw);
+        return e;
     }
     template <typename T>
     cudaError_t get(T **p, size_t count) {
@@ -251,43 +271,46 @@ int cgnn_compress_csr_batch(const int64_t *vlist, const int64_t *elist, int64_t 
     Arena arena;
     int32_t *rowptr[2], *sym[2], *row_of[2], *keep, *value, *slot, *run_count, *flag, *cand_count, *uses, *remap;
     uint64_t *key, *key_sorted, *run_key, *cand_key, *weight;
-    uint8_t *take;
+    uint8_t *take, *temp;
     int32_t *scalars;  // 0: bad input, 1: runs, 2: candidates, 3: new total, 4: rules kept
-    for (int b = 0; b < 2; ++b) {
-        CGNN_CUDA(arena.get(&rowptr[b], (size_t)n + 1));
-        CGNN_CUDA(arena.get(&sym[b], (size_t)cap));
-        CGNN_CUDA(arena.get(&row_of[b], (size_t)cap));
-    }
-    CGNN_CUDA(arena.get(&keep, (size_t)cap));
-    CGNN_CUDA(arena.get(&value, (size_t)cap));
-    CGNN_CUDA(arena.get(&slot, (size_t)cap));
-    CGNN_CUDA(arena.get(&run_count, (size_t)cap));
-    CGNN_CUDA(arena.get(&flag, (size_t)cap));
-    CGNN_CUDA(arena.get(&key, (size_t)cap));
-    CGNN_CUDA(arena.get(&key_sorted, (size_t)cap));
-    CGNN_CUDA(arena.get(&run_key, (size_t)cap));
-    CGNN_CUDA(arena.get(&weight, (size_t)cap));
-    CGNN_CUDA(arena.get(&take, (size_t)cap));
-    CGNN_CUDA(arena.get(&scalars, 8));
-    CGNN_CUDA(cudaMemsetAsync(scalars, 0, 8 * sizeof(int32_t), stream));
-    // candidate arrays are sized per round (at most one candidate per min_frequency pairs)
+    // candidate arrays: at most one candidate per min_frequency pairs
     const size_t cand_cap = (size_t)(cap / min_frequency + 1);
-    CGNN_CUDA(arena.get(&cand_key, cand_cap));
-    CGNN_CUDA(arena.get(&cand_count, cand_cap));
-    CGNN_CUDA(arena.get(&uses, cand_cap));
-    CGNN_CUDA(arena.get(&remap, cand_cap));
-    int32_t *used = flag, *rank = slot;  // free again once the rows are compacted
-
     size_t temp_bytes = 0, need = 0;
     const int cap32 = (int)std::max<int64_t>(cap, 1);
-    cub::DeviceRadixSort::SortKeys(nullptr, need, key, key_sorted, cap32, 0, 64, stream);
-    temp_bytes = std::max(temp_bytes, need);
-    cub::DeviceRunLengthEncode::Encode(nullptr, need, key_sorted, run_key, run_count, scalars + 1, cap32, stream);
-    temp_bytes = std::max(temp_bytes, need);
-    cub::DeviceScan::ExclusiveSum(nullptr, need, flag, slot, cap32, stream);
-    temp_bytes = std::max(temp_bytes, need);
-    uint8_t *temp;
-    CGNN_CUDA(arena.get(&temp, temp_bytes));
+    for (int pass = 0; pass < 2; ++pass) {  // 0: sizes only, 1: pointers into the one allocation
+        for (int b = 0; b < 2; ++b) {
+            arena.carve(&rowptr[b], (size_t)n + 1);
+            arena.carve(&sym[b], (size_t)cap);
+            arena.carve(&row_of[b], (size_t)cap);
+        }
+        arena.carve(&keep, (size_t)cap);
+        arena.carve(&value, (size_t)cap);
+        arena.carve(&slot, (size_t)cap);
+        arena.carve(&run_count, (size_t)cap);
+        arena.carve(&flag, (size_t)cap);
+        arena.carve(&key, (size_t)cap);
+        arena.carve(&key_sorted, (size_t)cap);
+        arena.carve(&run_key, (size_t)cap);
+        arena.carve(&weight, (size_t)cap);
+        arena.carve(&take, (size_t)cap);
+        arena.carve(&scalars, 8);
+        arena.carve(&cand_key, cand_cap);
+        arena.carve(&cand_count, cand_cap);
+        arena.carve(&uses, cand_cap);
+        arena.carve(&remap, cand_cap);
+        if (pass == 0) {
+            cub::DeviceRadixSort::SortKeys(nullptr, need, key, key_sorted, cap32, 0, 64, stream);
+            temp_bytes = std::max(temp_bytes, need);
+            cub::DeviceRunLengthEncode::Encode(nullptr, need, key_sorted, run_key, run_count, scalars + 1, cap32, stream);
+            temp_bytes = std::max(temp_bytes, need);
+            cub::DeviceScan::ExclusiveSum(nullptr, need, flag, slot, cap32, stream);
+            temp_bytes = std::max(temp_bytes, need);
+        }
+        arena.carve(&temp, temp_bytes);
+        if (pass == 0) CGNN_CUDA(arena.commit());
+    }
+    CGNN_CUDA(cudaMemsetAsync(scalars, 0, 8 * sizeof(int32_t), stream));
+    int32_t *used = flag, *rank = slot;  // free again once the rows are compacted
 
     load_rows_kernel<<<blocks_for(std::max(n + 1, cap)), THREADS, 0, stream>>>(vlist, elist, n, cap, rowptr[0], sym[0],
                                                                               scalars);
