@@ -849,8 +849,9 @@ def measure_gcn(graph, e_orig, steps, warmup, world, rank, device, widths=(16, 6
     (use_transformation=True, H=16, refresh_interval=5) on the config-2 graph (already on `device`),
     47 uniform classes, input feature width swept over 16/64/256/1024.  A step = one training epoch
     (forward, NLL loss on all nodes, backward, Adam step), timed after warm-up epochs as the reference's
-    benchmark/end2end/compressgnn_gcn.py does.  With N GPUs the feature columns of every layer are
-    sharded (strong scaling: the same model and matrix on more GPUs) and the graph is replicated."""
+    benchmark/end2end/compressgnn_gcn.py does.  With N GPUs the same model and matrix run with the feature
+    columns of every layer sharded when the input has 512 columns or more, else as one replica per GPU
+    (`dist.place_model`); the graph is replicated either way."""
     import torch
     import torch.distributed as dist
     from compressgnn_b200.model import GCN
@@ -867,11 +868,11 @@ def measure_gcn(graph, e_orig, steps, warmup, world, rank, device, widths=(16, 6
         model = GCN(width, 47, hidden_features=128, param_H=16, dropout=0.3, use_transformation=True,
                     refresh_interval=5, num_layers=2).to(device)
         opt = torch.optim.Adam(model.parameters(), lr=1e-3)
-        if world > 1:
+        # N > 1: column-sharded from 512 input columns up (shares the parameters of `model`), a replica on
+        # every rank below that, where the collectives of a sharded epoch cost more than the shards save
+        net, sharded = cdist.place_model(model, width, dist.group.WORLD if world > 1 else None)
+        if sharded:
             x = cdist.shard_columns(x, rank, world)
-            net = cdist.ShardedGCN(model, dist.group.WORLD)  # shares the parameters of `model`
-        else:
-            net = model
 
         def epoch(e):
             net.set_epoch(e)
@@ -901,9 +902,10 @@ def measure_gcn(graph, e_orig, steps, warmup, world, rank, device, widths=(16, 6
             t = torch.tensor([ms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
-        if world > 1:
+        if sharded:
             net.consolidate_parameters()
-        report[str(width)] = {"epoch_ms": ms, "final_loss": float(loss.detach())}
+        report[str(width)] = {"epoch_ms": ms, "final_loss": float(loss.detach()),
+                              "placement": "columns sharded" if sharded else ("replica per GPU" if world > 1 else "one GPU")}
         del model, net, opt, x
     rt.raise_on_device_status()
     return {"metric": "gcn_epoch_ms", "unit": "ms", "steps": steps, "warmup": max(warmup, 3), "n_gpus": world,
@@ -911,8 +913,10 @@ def measure_gcn(graph, e_orig, steps, warmup, world, rank, device, widths=(16, 6
             "config": {"workload": "gcn: 2-layer GCN, propagation + transformation compression, config-2 graph",
                        "nodes": n, "orig_edges": e_orig, "rules": graph.rule_cnt, "levels": graph.step, "classes": 47,
                        "hidden": 128, "bits": 16, "refresh_interval": 5, "compressor": COMPRESS,
-                       "parallelism": f"feature columns of every layer sharded over {world} GPU(s), graph replicated; "
-                                      "collectives: projection all-reduce on refresh epochs; per hidden layer and "
+                       "parallelism": f"{world} GPU(s), graph replicated; inputs of 512 columns and more: feature "
+                                      "columns of every layer sharded; narrower inputs: one replica per GPU, no "
+                                      "collective (`placement` per width); collectives of a sharded epoch: "
+                                      "projection all-reduce on refresh epochs; per hidden layer and "
                                       "epoch one all-gather of the representatives and one reduce-scatter of "
                                       "their gradient; no weight-gradient exchange (each rank steps on the "
                                       "weight rows it owns)"},

@@ -211,3 +211,23 @@ class ShardedGCN(torch.nn.Module):
         for g in grads:
             g.copy_(flat[offset:offset + g.numel()].view_as(g))
             offset += g.numel()
+
+
+# Input width from which sharding a model's feature columns pays on one node.  Every epoch of a sharded
+# model issues two collectives per hidden layer and a dozen more small launches; measured on B200s that
+# is 0.3-0.5 ms per epoch, which the shard-local operators only win back when the first layer's work
+# (proportional to the input width) is several times that: 1024 input columns gain at 2, 4 and 8 GPUs,
+# 256 and fewer lose at every GPU count.
+MIN_SHARDED_FEATURES = 512
+
+
+def place_model(model, in_features, group=None, min_features=MIN_SHARDED_FEATURES):
+    """``(module, sharded)``: a ``ShardedGCN`` over ``model`` when the input is wide enough for column
+    sharding to pay, else ``model`` itself, to be run as a replica on every rank (the full feature matrix,
+    the same parameters and the same random stream everywhere, no collective).  A sharded module takes
+    ``shard_columns(x, rank, world)``, a replica takes ``x``."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world > 1 and in_features >= min_features and in_features % world == 0:
+        return ShardedGCN(model, group), True
+    return model, False
+

@@ -96,6 +96,12 @@ def _gather_worker(rank, world, port):
         gathered = cdist.gather_columns_autograd(local, None, replicated_consumer=True)
         ((gathered @ weight.t() - target) ** 2).sum().backward()
         torch.testing.assert_close(local.grad, ref_in.grad[:, begin:end])
+        # (c) a model is sharded only from 512 input columns up (and only when the columns divide)
+        from compressgnn_b200.model import GCN
+        for width, want in ((1024, True), (512, True), (256, False), (16, False), (513, False)):
+            model = GCN(width, 5, hidden_features=16, param_H=4, use_transformation=True, num_layers=2)
+            net, sharded = cdist.place_model(model, width)
+            assert sharded == want and isinstance(net, cdist.ShardedGCN) == want and (sharded or net is model)
     finally:
         dist.destroy_process_group()
 
