@@ -867,7 +867,7 @@ def measure_gcn(graph, e_orig, steps, warmup, world, rank, device, widths=(16, 6
         torch.manual_seed(5)
         model = GCN(width, 47, hidden_features=128, param_H=16, dropout=0.3, use_transformation=True,
                     refresh_interval=5, num_layers=2).to(device)
-        opt = torch.optim.Adam(model.parameters(), lr=1e-3)
+        opt = torch.optim.Adam(model.parameters(), lr=1e-3, fused=True)  # one kernel for all parameters
         # N > 1: column-sharded from 512 input columns up (shares the parameters of `model`), a replica on
         # every rank below that, where the collectives of a sharded epoch cost more than the shards save
         net, sharded = cdist.place_model(model, width, dist.group.WORLD if world > 1 else None)
@@ -912,7 +912,8 @@ def measure_gcn(graph, e_orig, steps, warmup, world, rank, device, widths=(16, 6
             "scaling": "strong", "higher_is_better": False, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "gcn: 2-layer GCN, propagation + transformation compression, config-2 graph",
                        "nodes": n, "orig_edges": e_orig, "rules": graph.rule_cnt, "levels": graph.step, "classes": 47,
-                       "hidden": 128, "bits": 16, "refresh_interval": 5, "compressor": COMPRESS,
+                       "hidden": 128, "bits": 16, "refresh_interval": 5, "optimizer": "torch.optim.Adam(lr=1e-3, fused=True)",
+                       "compressor": COMPRESS,
                        "parallelism": f"{world} GPU(s), graph replicated; inputs of 512 columns and more: feature "
                                       "columns of every layer sharded; narrower inputs: one replica per GPU, no "
                                       "collective (`placement` per width); collectives of a sharded epoch: "

@@ -54,7 +54,7 @@ def _whole_pass(graph, x, backward, record, out, rule_out):
         raise RuntimeError("out does not match the graph and the feature matrix")
     if out.numel() == 0:
         return out
-    with torch.cuda.device(x.device):
+    with _native.on_device(x.device):
         if record is None:
             return _native.propagate_pass(table, x, rule_out, out)
         last = table["n"] - 1

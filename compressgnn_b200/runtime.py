@@ -33,8 +33,39 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr()) if t is not None and t.numel() else ctypes.c_void_p(0)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_ptr(device):
+    """The current CUDA stream of ``device`` as the integer the C ABI takes."""
+    if _raw_stream is not None:  # no Stream object per call: a training epoch asks a hundred times
+        device = torch.device(device)
+        return _raw_stream(device.index if device.index is not None else torch.cuda.current_device())
     return torch.cuda.current_stream(device).cuda_stream
+
+
+class on_device:
+    """``with on_device(d):`` makes ``d`` the current CUDA device for the native calls inside, like
+    ``torch.cuda.device(d)``, but does nothing at all when it already is (the usual case)."""
+    __slots__ = ("index", "previous")
+
+    def __init__(self, device):
+        device = torch.device(device)
+        self.index = device.index if device.index is not None else torch.cuda.current_device()
+        self.previous = -1
+
+    def __enter__(self):
+        current = torch.cuda.current_device()
+        if current != self.index:
+            self.previous = current
+            torch.cuda.set_device(self.index)
+        return self
+
+    def __exit__(self, *exc):
+        if self.previous >= 0:
+            torch.cuda.set_device(self.previous)
+            self.previous = -1
+        return False
 
 
 def _dtype_code(t, what="tensor"):
@@ -95,7 +126,7 @@ class SegmentPlan:
                      col1.device == device, "plan: the two blocks must share rows, dtype and device")
             rowptr1, col1 = rowptr1.contiguous(), col1.contiguous()
         handle = ctypes.c_void_p(0)
-        with torch.cuda.device(device):
+        with on_device(device):
             check(lib().cgnn_plan_create(
                 ctypes.byref(handle), rowptr.numel() - 1, rowptr.element_size(),
                 ctypes.c_void_p(rowptr.data_ptr()), _ptr(col), col.numel(),
@@ -110,7 +141,7 @@ class SegmentPlan:
         _require(index.is_cuda and index.dtype == torch.int64 and index.dim() == 1 and
                  index.is_contiguous(), "Expected contiguous int64 index on input device")
         handle = ctypes.c_void_p(0)
-        with torch.cuda.device(index.device):
+        with on_device(index.device):
             check(lib().cgnn_plan_create_from_index(ctypes.byref(handle), _ptr(index), index.numel(),
                                                     int(groups), int(split),
                                                     _stream_ptr(index.device)))
@@ -125,7 +156,7 @@ class SegmentPlan:
             _require(sum(t.numel() for t in tensors) == self.nnz, "values do not match the plan's entries")
             cached = torch.empty(self.nnz, dtype=val0.dtype, device=self.device)
             if self.nnz:
-                with torch.cuda.device(self.device):
+                with on_device(self.device):
                     check(lib().cgnn_plan_permute_values(
                         self.handle, _dtype_code(val0, "values"), _ptr(val0.contiguous()),
                         _ptr(val1.contiguous()) if val1 is not None else None, _ptr(cached),
@@ -235,7 +266,7 @@ def spmm_with_plan(plan, value, mat, out=None, accumulate=False):
     sp, sb = plan.scratch(width, code)
     if value is not None:
         value = plan.values(value)
-    with torch.cuda.device(mat.device):
+    with on_device(mat.device):
         check(lib().cgnn_spmm(plan.handle, code, width, _ptr(value), _ptr(mat), _ptr(out),
                               1 if accumulate else 0, sp, sb, _stream_ptr(mat.device)))
     return out
@@ -268,7 +299,7 @@ def spmm_pair_with_plan(plan, value0, mat0, value1, mat1, out=None, accumulate=F
                  f"{mat.size(0)} rows")
     sp, sb = plan.scratch(width, code)
     value = plan.values(value0, value1)
-    with torch.cuda.device(mat0.device):
+    with on_device(mat0.device):
         check(lib().cgnn_spmm_pair(plan.handle, code, width, _ptr(value), _ptr(mat0), _ptr(mat1),
                                    _ptr(out), 1 if accumulate else 0, sp, sb,
                                    _stream_ptr(mat0.device)))
@@ -367,7 +398,7 @@ def project(input, planes):
     _require(planes.device == input.device and planes.dtype == input.dtype and
              planes.size(0) == input.size(1), "Hash plane shape/device/dtype mismatch")
     proj = torch.empty((input.size(0), bits), dtype=input.dtype, device=input.device)
-    with torch.cuda.device(input.device):
+    with on_device(input.device):
         check(lib().cgnn_cluster_project(_dtype_code(input), _ptr(input), _ptr(planes),
                                          input.size(0), input.size(1), bits, _ptr(proj),
                                          _stream_ptr(input.device)))
@@ -418,7 +449,7 @@ def cluster_assign(input, planes, bits, workspace):
     if n == 0:
         return (torch.empty(0, dtype=torch.int64, device=device),
                 torch.zeros(1, dtype=torch.int32, device=device), 0)
-    with torch.cuda.device(device):
+    with on_device(device):
         codes = torch.empty(n, dtype=torch.int32, device=device)
         check(lib().cgnn_cluster_codes(_dtype_code(input), _ptr(input), _ptr(planes), n,
                                        input.size(1), bits, _ptr(codes), _stream_ptr(device)))
@@ -433,7 +464,7 @@ def cluster_assign_from_projection(proj, workspace):
     if n == 0:
         return (torch.empty(0, dtype=torch.int64, device=device),
                 torch.zeros(1, dtype=torch.int32, device=device), 0)
-    with torch.cuda.device(device):
+    with on_device(device):
         codes = torch.empty(n, dtype=torch.int32, device=device)
         check(lib().cgnn_cluster_codes_from_projection(_dtype_code(proj), _ptr(proj), n, bits,
                                                        _ptr(codes), _stream_ptr(device)))
@@ -470,7 +501,7 @@ def cluster_mean(input, index, count, plan=None):
     _require(plan.rows == groups and plan.nnz == index.numel(), "cluster_mean: plan does not match index/count")
     code = _dtype_code(input)
     sp, sb = plan.scratch(width, code)
-    with torch.cuda.device(input.device):
+    with on_device(input.device):
         check(lib().cgnn_cluster_mean(plan.handle, code, width, _ptr(input), _ptr(count), _ptr(out),
                                       sp, sb, _stream_ptr(input.device)))
     return out
@@ -485,7 +516,7 @@ def cluster_mean_backward(grad, index, count):
     out = torch.empty((index.numel(), grad.size(1)), dtype=grad.dtype, device=grad.device)
     if out.numel() == 0:
         return out
-    with torch.cuda.device(grad.device):
+    with on_device(grad.device):
         scaled = torch.empty_like(grad)  # grad / count, divided once per group row
         check(lib().cgnn_cluster_mean_backward(_dtype_code(grad), index.numel(), grad.size(1),
                                                grad.size(0), _ptr(grad), _ptr(index), _ptr(count),
@@ -509,7 +540,7 @@ def cluster_reconstruct(reps, index, bias, relu, dropout_p=0.0, seed=0):
     dropout_p = float(dropout_p)
     _require(0.0 <= dropout_p < 1.0, "dropout probability must lie in [0, 1)")
     _require(dropout_p == 0.0 or relu, "the fused dropout follows a ReLU (the backward reads its mask off the zeros)")
-    with torch.cuda.device(reps.device):
+    with on_device(reps.device):
         if dropout_p > 0.0:
             check(lib().cgnn_cluster_reconstruct_dropout(
                 _dtype_code(reps), index.numel(), reps.size(1), reps.size(0), _ptr(reps), _ptr(index), _ptr(bias),
@@ -549,7 +580,7 @@ def cluster_reconstruct_backward(grad, index, output, groups, relu, plan=None,
              "cluster_reconstruct_backward: plan does not match index/groups")
     code = _dtype_code(grad)
     sp, sb = plan.scratch(width, code)
-    with torch.cuda.device(grad.device):
+    with on_device(grad.device):
         check(lib().cgnn_cluster_reconstruct_backward(
             plan.handle, code, width, _ptr(grad), _ptr(output),
             (2 if output_is_forward_result else 1) if relu else 0, _ptr(out),
@@ -579,7 +610,7 @@ def compress_csr_batch(vlist, elist, rounds=12, min_pair_frequency=16):
     vlist, elist = vlist.contiguous(), elist.contiguous()
     device = vlist.device
     handle = ctypes.c_void_p(0)
-    with torch.cuda.device(device):
+    with on_device(device):
         stream = _stream_ptr(device)
         check(lib().cgnn_compress_csr_batch(_ptr(vlist), _ptr(elist), vlist.numel() - 1, int(rounds),
                                             int(min_pair_frequency), ctypes.byref(handle), stream))
