@@ -295,6 +295,13 @@ class Compressgnn_Cluster(torch.nn.Module):
         return Assignment(index, counts, active, signature, self._schedule.epoch)
 
     def forward(self, input, epoch=None, cache_key=None, force_refresh=False):
+        kept = self.assignment(input, epoch=epoch, cache_key=cache_key, force_refresh=force_refresh)
+        reps = _Mean.apply(input, kept.index, kept.counts)
+        return (reps, kept.index) if self.is_training else reps
+
+    def assignment(self, input, epoch=None, cache_key=None, force_refresh=False):
+        """The bucket assignment ``forward`` would use for ``input`` now (kept or recomputed, by the same
+        rules), without the means: ``.index`` int64[N], ``.counts`` int32[active + 1], ``.active``."""
         self._check_input(input)
         if epoch is not None:
             self.set_epoch(epoch)
@@ -318,5 +325,4 @@ class Compressgnn_Cluster(torch.nn.Module):
             if self.cache and clock.epoch is not None:
                 self._kept.keep(slot, kept)
         self.vertex_index, self.active_bucket = kept.index, kept.active
-        reps = _Mean.apply(input, kept.index, kept.counts)
-        return (reps, kept.index) if self.is_training else reps
+        return kept

@@ -7,7 +7,51 @@ import torch
 import torch.nn.functional as F
 from torch import Tensor
 
+from torch.autograd.function import once_differentiable
+
+from . import runtime as _native
 from .layer import Compressgnn_Cluster, Compressgnn_Reconstruct, KPropagate
+
+
+class _TransformedLinear(torch.autograd.Function):
+    """``act(dropout)(Linear(bucket means of x))`` spread back over the nodes -- cluster mean, the Linear on
+    the representatives and the fused reconstruction as ONE autograd node (ref: the three modules chained
+    in model/compressgnn/gcn.py:27-34).  Same native calls and the same arithmetic as the modules one by
+    one; what goes away is four autograd nodes per layer and direction, which is host time an epoch of
+    ~1.5 ms is bound by."""
+
+    @staticmethod
+    def forward(ctx, x, index, counts, weight, bias, relu, dropout_p):
+        x = x.contiguous()
+        reps = _native.cluster_mean(x, index, counts)
+        lin = reps @ weight.t()
+        seed = 0
+        if dropout_p > 0.0:
+            seed = int(torch.randint(0, 2**63 - 1, (1,), dtype=torch.int64).item())
+        out = _native.cluster_reconstruct(lin, index, bias, relu, dropout_p, seed)
+        ctx.save_for_backward(index, counts, reps, weight, out)
+        ctx.relu, ctx.dropout_p = relu, dropout_p
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, grad):
+        index, counts, reps, weight, out = ctx.saved_tensors
+        dropped = ctx.dropout_p > 0.0
+        # without dropout the rows of a group are identical and one mask row per group suffices; with it
+        # every row has its own zeros (dropped or clamped alike): exact mask, sums rescaled
+        d_lin, d_bias = _native.cluster_reconstruct_backward(grad.contiguous(), index, out, reps.size(0), ctx.relu,
+                                                             return_bias_grad=True,
+                                                             output_is_forward_result=not dropped)
+        if dropped:
+            scale = 1.0 / (1.0 - ctx.dropout_p)
+            d_lin.mul_(scale)
+            d_bias.mul_(scale)
+        d_weight = d_lin.t() @ reps if ctx.needs_input_grad[3] else None
+        d_x = None
+        if ctx.needs_input_grad[0]:
+            d_x = _native.cluster_mean_backward(d_lin @ weight, index, counts)
+        return d_x, None, None, d_weight, d_bias if ctx.needs_input_grad[4] else None, None, None
 
 
 class GNNLayer(torch.nn.Module):
@@ -36,6 +80,11 @@ class GNNLayer(torch.nn.Module):
         """``dropout``: probability of the dropout the model applies to this layer's (ReLU) output; with the
         transformation path it runs inside the reconstruct kernel."""
         x = self.P(x=x, edge_index=edge_index, edge_weight=edge_weight, vertex_cnt=vertex_cnt, rule_cnt=rule_cnt)
+        if self.use_transformation and x.is_cuda and x.dim() == 2 and self.cluster.is_training and \
+                (self.activation == "relu" or not dropout):
+            kept = self.cluster.assignment(x)
+            return _TransformedLinear.apply(x, kept.index, kept.counts, self.lin.weight, self.lin.bias,
+                                            self.activation == "relu", float(dropout))
         if self.use_transformation:
             reps, index = self.cluster(x)
             fused = dropout if self.activation == "relu" else 0.0
