@@ -45,11 +45,15 @@ Rows rows_from_csr(const int64_t *vlist, const int64_t *elist, int64_t total) {
     return g;
 }
 
-// graphT[x] lists, in ascending v and with multiplicity, the rows v that contain x.
-Rows referencing_rows(const int64_t *vlist, const int64_t *elist, int64_t total) {
+// graphT[x] lists, in ascending v and with multiplicity, the rows v that contain rule x (x >= n).  The
+// reference keeps these lists for vertices as well and splices them on every inlining
+// (filter.h:31-67); nothing ever reads a vertex's list -- neither a decision nor the output -- and with
+// hubs in thousands of rows those splices were most of the run time, so they are not kept here.
+Rows referencing_rows(const int64_t *vlist, const int64_t *elist, int64_t total, int64_t n) {
     Rows t((size_t)total);
     for (int64_t v = 0; v < total; ++v)
-        for (int64_t e = vlist[v]; e < vlist[v + 1]; ++e) t[elist[e]].push_back(v);
+        for (int64_t e = vlist[v]; e < vlist[v + 1]; ++e)
+            if (elist[e] >= n) t[elist[e]].push_back(v);
     return t;
 }
 
@@ -64,7 +68,7 @@ void splice_first(std::vector<int64_t> &list, int64_t id, const std::vector<int6
 // Inline rule `id` into every row that references it and hand its references to its
 // children (ref: mergeRule, src/offline/csrc/filter.h:31-67, depth_filter.h:17-40).
 template <typename ParentHook, typename ChildHook>
-void inline_rule(int64_t id, Rows &graph, Rows &graphT, ParentHook on_parent, ChildHook on_child) {
+void inline_rule(int64_t id, int64_t n, Rows &graph, Rows &graphT, ParentHook on_parent, ChildHook on_child) {
     const std::vector<int64_t> body = graph[id];
     const std::vector<int64_t> parents = graphT[id];
     for (int64_t node : parents) {
@@ -72,7 +76,7 @@ void inline_rule(int64_t id, Rows &graph, Rows &graphT, ParentHook on_parent, Ch
         on_parent(node, (int64_t)body.size());
     }
     for (int64_t child : body) {
-        splice_first(graphT[child], id, parents);
+        if (child >= n) splice_first(graphT[child], id, parents);
         on_child(child);
     }
 }
@@ -397,7 +401,7 @@ CGNN_HOST_API int cgnn_host_filter_csr(const int64_t *vlist, const int64_t *elis
                                        int threshold, Result **out) {
     const int64_t total = n + r;
     Rows graph = rows_from_csr(vlist, elist, total);
-    Rows graphT = referencing_rows(vlist, elist, total);
+    Rows graphT = referencing_rows(vlist, elist, total, n);
     std::vector<int> len((size_t)r), freq((size_t)r);
     std::vector<char> removed((size_t)r);
     auto judge = [&](int l, int f) { return (f - 1) * (l - 1) - 1 <= threshold; };
@@ -409,7 +413,7 @@ CGNN_HOST_API int cgnn_host_filter_csr(const int64_t *vlist, const int64_t *elis
     for (int64_t i = 0; i < r; ++i) {
         if (!removed[i]) continue;
         inline_rule(
-            i + n, graph, graphT,
+            i + n, n, graph, graphT,
             [&](int64_t node, int64_t body) {
                 if (node >= n) {
                     len[node - n] += (int)(body - 1);
@@ -436,7 +440,7 @@ CGNN_HOST_API int cgnn_host_depth_filter_csr(const int64_t *vlist, const int64_t
                                              int64_t r, int max_depth, int min_edge, Result **out) {
     const int64_t total = n + r;
     Rows graph = rows_from_csr(vlist, elist, total);
-    Rows graphT = referencing_rows(vlist, elist, total);
+    Rows graphT = referencing_rows(vlist, elist, total, n);
     std::vector<int> depth;
     int m_depth = rule_depths(vlist, elist, n, r, depth);
     for (int64_t i = 0; i < r; ++i)
@@ -451,7 +455,7 @@ CGNN_HOST_API int cgnn_host_depth_filter_csr(const int64_t *vlist, const int64_t
         }
         for (int64_t i = 0; i < r; ++i)
             if (depth[n + i] == m_depth) {
-                inline_rule(i + n, graph, graphT, [](int64_t, int64_t) {}, [](int64_t) {});
+                inline_rule(i + n, n, graph, graphT, [](int64_t, int64_t) {}, [](int64_t) {});
                 removed[i] = 1;
             }
         --m_depth;
