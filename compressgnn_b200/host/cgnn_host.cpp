@@ -404,11 +404,11 @@ CGNN_HOST_API int cgnn_host_filter_csr(const int64_t *vlist, const int64_t *elis
     Rows graphT = referencing_rows(vlist, elist, total, n);
     std::vector<int> len((size_t)r), freq((size_t)r);
     std::vector<char> removed((size_t)r);
-    auto judge = [&](int l, int f) { return (f - 1) * (l - 1) - 1 <= threshold; };
+    auto not_worth_keeping = [&](int l, int f) { return (f - 1) * (l - 1) - 1 <= threshold; };
     for (int64_t i = 0; i < r; ++i) {
         freq[i] = (int)graphT[i + n].size();
         len[i] = (int)graph[i + n].size();
-        removed[i] = judge(len[i], freq[i]);
+        removed[i] = not_worth_keeping(len[i], freq[i]);
     }
     for (int64_t i = 0; i < r; ++i) {
         if (!removed[i]) continue;
@@ -417,14 +417,14 @@ CGNN_HOST_API int cgnn_host_filter_csr(const int64_t *vlist, const int64_t *elis
             [&](int64_t node, int64_t body) {
                 if (node >= n) {
                     len[node - n] += (int)(body - 1);
-                    removed[node - n] = judge(len[node - n], freq[node - n]);
+                    removed[node - n] = not_worth_keeping(len[node - n], freq[node - n]);
                 }
             },
             [&](int64_t child) {
                 if (child >= n) {
                     // The reference adds the whole new reference count, not the delta.
                     freq[child - n] += (int)graphT[child].size();
-                    removed[child - n] = judge(len[child - n], freq[child - n]);
+                    removed[child - n] = not_worth_keeping(len[child - n], freq[child - n]);
                 }
             });
     }
