@@ -59,6 +59,13 @@ SIGNATURES = {
                                                   ctypes.c_double, ctypes.c_uint64, _c_ptr, _c_ptr]),
     "cgnn_cluster_reconstruct_backward": (_c_int, [_c_ptr, _c_int, _c_i64, _c_ptr, _c_ptr, _c_int,
                                                    _c_ptr, _c_ptr, _c_ptr, _c_size, _c_ptr]),
+    "cgnn_sample_seed": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr]),
+    "cgnn_sample_count": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr]),
+    "cgnn_sample_pick": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_i64, _c_i64, _c_ptr, _c_ptr, ctypes.c_uint32,
+                                  ctypes.c_uint64, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
+    "cgnn_sample_claim": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_ptr, _c_ptr]),
+    "cgnn_sample_relabel": (_c_int, [_c_ptr, _c_i64, _c_i64, _c_ptr, _c_ptr, _c_i64, _c_ptr, _c_ptr, _c_ptr,
+                                     _c_ptr, _c_ptr]),
     "cgnn_compress_csr_batch": (_c_int, [_c_ptr, _c_ptr, _c_i64, _c_int, _c_int, _c_ptr, _c_ptr]),
     "cgnn_compressed_info": (_c_int, [_c_ptr, _c_ptr]),
     "cgnn_compressed_copy": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_ptr]),

@@ -104,6 +104,10 @@ cudaError_t pool_alloc(void **ptr, size_t bytes, cudaStream_t stream) {
 
 }  // namespace cgnn
 
+namespace cgnn {
+int sample_status(int *out);  // cgnn_sample.cu
+}
+
 extern "C" {
 
 int cgnn_version(void) { return 100; }
@@ -117,7 +121,9 @@ int cgnn_device_status(int *status_out) {
     int rc = cgnn::segreduce_status(&a);
     if (rc == CGNN_OK) rc = cgnn::gather_status(&b);
     if (rc == CGNN_OK) rc = cgnn::cluster_status(&c);
-    *status_out = a | b | c;
+    int d = 0;
+    if (rc == CGNN_OK) rc = cgnn::sample_status(&d);  // defined in cgnn_sample.cu
+    *status_out = a | b | c | d;
     return rc;
 }
 

@@ -280,6 +280,49 @@ int cgnn_compressed_copy(const cgnn_compressed *c, int32_t *vlist_out, int32_t *
                          cgnn_stream_t stream);
 void cgnn_compressed_destroy(cgnn_compressed *c);
 
+/* ---------------------------------------------------------------------------------------
+ * Neighbour sampling on the compressed graph, one hop at a time.
+ * ref: neighbor_sample_sim_impl, src/sample/csrc/neighbor_sample.h:27-131 (a host function there, bound
+ * as compressgnn_sample.neighbor_sample_cg_sim); get_neighbor / get_neighbor_list,
+ * src/sample/csrc/storage_api.h:7-118.  Same result contract: `samples` (seeds first, then new nodes in
+ * the order they are first seen), and per sampled edge the local id of the frontier node and of the
+ * neighbour.  The random neighbour indices come from a counter-based generator under `seed`.
+ *
+ * All arrays are device arrays.  The graph is given by the CSR blocks CompressGraph holds (int64), with
+ * the rule -> rule levels merged into one CSR, and the two degree arrays of gen_degree.
+ * A hop over the frontier samples[begin, begin + frontier):
+ *   cgnn_sample_count   count[i] = min(fanout, degree)  (degree when fanout >= degree)
+ *   (caller: offset = exclusive scan of count, total = its sum)
+ *   cgnn_sample_pick    picked[offset[i]..] = the neighbours, source[..] = begin + i; scratch: total int64
+ *   cgnn_sample_claim   first[] / is_new[]: which pick introduces a vertex that has no local id yet
+ *   (caller: rank = exclusive scan of is_new, new = its sum; samples must have room for end + new)
+ *   cgnn_sample_relabel target[p] = local id of picked[p]; appends the new vertices to samples from `end`;
+ *                       records their ids in local_of and restores first[] to INT32_MAX
+ * local_of and first are int32[vertices], filled with INT32_MAX before the first hop;
+ * cgnn_sample_seed enters the seeds (samples[0, count)) into local_of.  A vertex outside [0, vertices)
+ * or a degree table that does not match the graph sets bits 1 / 4 of cgnn_device_status; nothing traps. */
+typedef struct {
+    const int64_t *v2v_ptr, *v2v_col;   /* [vertices + 1], direct neighbours */
+    const int64_t *v2r_ptr, *v2r_col;   /* [vertices + 1], rules a vertex lists */
+    const int64_t *r2v_ptr, *r2v_col;   /* [rules + 1], vertices a rule lists itself */
+    const int64_t *r2r_ptr, *r2r_col;   /* [rules + 1], rules a rule lists (all levels merged) */
+    const int64_t *vertex_degree, *rule_degree;
+    int64_t vertices, rules;
+} cgnn_sample_graph;
+int cgnn_sample_seed(const int64_t *samples, int64_t count, int64_t vertices, int32_t *local_of,
+                     cgnn_stream_t stream);
+int cgnn_sample_count(const cgnn_sample_graph *graph, const int64_t *samples, int64_t begin,
+                      int64_t frontier, int64_t fanout, int64_t *count, cgnn_stream_t stream);
+int cgnn_sample_pick(const cgnn_sample_graph *graph, const int64_t *samples, int64_t begin,
+                     int64_t frontier, int64_t fanout, const int64_t *count, const int64_t *offset,
+                     uint32_t hop, uint64_t seed, int64_t *picked, int64_t *source, int64_t *scratch,
+                     cgnn_stream_t stream);
+int cgnn_sample_claim(const int64_t *picked, int64_t total, int64_t vertices, const int32_t *local_of,
+                      int32_t *first, int64_t *is_new, cgnn_stream_t stream);
+int cgnn_sample_relabel(const int64_t *picked, int64_t total, int64_t vertices, const int64_t *is_new,
+                        const int64_t *rank, int64_t end, int32_t *local_of, int32_t *first,
+                        int64_t *target, int64_t *samples, cgnn_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

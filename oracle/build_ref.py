@@ -129,6 +129,31 @@ def build_offline(ref):
     return target
 
 
+def build_sample(ref):
+    """The reference's host neighbour sampler (``src/sample/csrc``: one translation unit over torch's
+    headers and the header-only hash map under ``third_party/parallel-hashmap``)."""
+    import torch
+    from torch.utils import cpp_extension
+
+    csrc = ref / "src" / "sample" / "csrc"
+    sources = [csrc / "function.cpp"]
+    target = OUT / "compressgnn_sample.so"
+    if _newer(target, sources + [csrc / "neighbor_sample.h", csrc / "storage_api.h"]):
+        return target
+    torch_lib = Path(torch.__file__).parent / "lib"
+    cmd = ["g++", "-O3", "-std=c++17", "-shared", "-fPIC", "-w", "-Wl,-Bsymbolic",
+           "-DTORCH_EXTENSION_NAME=compressgnn_sample", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           "-I", csrc, "-I", sysconfig.get_paths()["include"]]
+    for inc in cpp_extension.include_paths():
+        cmd += ["-isystem", inc]
+    cmd += sources
+    cmd += ["-L", torch_lib, f"-Wl,-rpath,{torch_lib}", "-lc10", "-ltorch", "-ltorch_cpu",
+            "-ltorch_python", "-o", target]
+    _run(cmd)
+    return target
+
+
 def build(reference_dir=DEFAULT_REFERENCE, quiet=False, with_cuda=False):
     """Compile both modules when the reference checkout exists; return what is usable."""
     ref = Path(reference_dir)
@@ -136,12 +161,15 @@ def build(reference_dir=DEFAULT_REFERENCE, quiet=False, with_cuda=False):
     if (ref / "src" / "runtime" / "csrc" / "function.cpp").is_file():
         build_runtime(ref)
         build_offline(ref)
+        if (ref / "src" / "sample" / "csrc" / "function.cpp").is_file() and \
+                (ref / "third_party" / "parallel-hashmap" / "parallel_hashmap" / "phmap.h").is_file():
+            build_sample(ref)
         if with_cuda:
             build_runtime_cuda(ref)
     elif not quiet:
         print("[oracle/_ref] reference checkout not found; using prebuilt files if present")
     return {name: (OUT / f"{name}.so").is_file()
-            for name in ("compressgnn_runtime", "compressgnn_offline")}
+            for name in ("compressgnn_runtime", "compressgnn_offline", "compressgnn_sample")}
 
 
 if __name__ == "__main__":

@@ -308,3 +308,149 @@ def reference_cuda_step(rt, graph, x, grad):
     gx = gpu_spmm(g.v2v_graph.csc(), grad, None, prefer_row=True)
     gx = gpu_spmm(g.r2v_graph.csc(), rule_g, gx, prefer_row=True)
     return out, gx
+
+
+# ---------------------------------------------------------------------------------------
+# Neighbour sampling on the compressed graph
+# ---------------------------------------------------------------------------------------
+def reference_sample_module():
+    """``compressgnn_sample`` built from the reference's own sources (``build_ref.py``), or ``None``."""
+    ref_dir = HERE / "_ref"
+    if not (ref_dir / "compressgnn_sample.so").is_file():
+        return None
+    if str(ref_dir) not in sys.path:
+        sys.path.insert(0, str(ref_dir))
+    try:
+        import torch  # noqa: F401  (libtorch symbols must be loaded first)
+        return __import__("compressgnn_sample")
+    except ImportError:
+        return None
+
+
+def philox_first_word(c0, c1, c2, c3, seed):
+    """First output word of Philox4x32 with 7 rounds (Salmon et al., SC 2011) for counter (c0..c3), key `seed`."""
+    mask = 0xFFFFFFFF
+    k0, k1 = seed & mask, (seed >> 32) & mask
+    for _ in range(7):
+        p0, p1 = 0xD2511F53 * c0, 0xCD9E8D57 * c2
+        c0, c1, c2, c3 = ((p1 >> 32) ^ c1 ^ k0) & mask, p1 & mask, ((p0 >> 32) ^ c3 ^ k1) & mask, p0 & mask
+        k0, k1 = (k0 + 0x9E3779B9) & mask, (k1 + 0xBB67AE85) & mask
+    return c0
+
+
+def exact_degrees(v2v, v2r, r2v, r2r_levels):
+    """``(vertex_degree, rule_degree)``: the number of vertices a rule expands to and the number of
+    neighbours of a vertex.  The level blocks are taken in the order topo_partition emits them (level 0:
+    rules whose children have no children), so that a child's size is final before its parents add it.
+    (gen_degree, src/offline/csrc/gen_degree.h:62-72, walks the levels from the last to the first and
+    agrees with this up to one level.)"""
+    r_degree = np.diff(r2v[0]).astype(np.int64)
+    for ptr, col in r2r_levels:
+        rows = np.repeat(np.arange(ptr.size - 1), np.diff(ptr))
+        np.add.at(r_degree, rows, r_degree[col])
+    v_degree = np.diff(v2v[0]).astype(np.int64)
+    rows = np.repeat(np.arange(v2r[0].size - 1), np.diff(v2r[0]))
+    np.add.at(v_degree, rows, r_degree[v2r[1]])
+    return v_degree, r_degree
+
+
+class CompressedNeighbors:
+    """Neighbour lists of a compressed graph given as ``(rowptr, col)`` blocks: a node's neighbours are its
+    v2v entries followed by the expansion of its v2r rules.  The children of a rule are taken from whichever
+    level block lists them (the reference indexes the levels by descent depth, storage_api.h:35-52 and
+    :94-107, which is the same block as long as the rule's children have no children themselves)."""
+
+    def __init__(self, v2v, v2r, r2v, r2r_levels, v_degree, r_degree):
+        (self.v2v_p, self.v2v_c), (self.v2r_p, self.v2r_c), (self.r2v_p, self.r2v_c) = v2v, v2r, r2v
+        self.levels, self.v_degree, self.r_degree = list(r2r_levels), v_degree, r_degree
+
+    def children(self, rule):
+        out = []
+        for ptr, col in self.levels:
+            out.extend(col[ptr[rule]:ptr[rule + 1]].tolist())
+        return out
+
+    def neighbor_list(self, node):
+        """All neighbours in list order (ref: get_neighbor_list, storage_api.h:72-118): v2v entries, then
+        the rules below the node breadth first, then every listed rule's own vertices."""
+        out = self.v2v_c[self.v2v_p[node]:self.v2v_p[node + 1]].tolist()
+        queue = self.v2r_c[self.v2r_p[node]:self.v2r_p[node + 1]].tolist()
+        head = 0
+        while head < len(queue):
+            queue.extend(self.children(queue[head]))
+            head += 1
+        for rule in queue:
+            out.extend(self.r2v_c[self.r2v_p[rule]:self.r2v_p[rule + 1]].tolist())
+        return out
+
+    def neighbor_at(self, node, index):
+        """The ``index``-th neighbour (ref: get_neighbor, storage_api.h:7-70): skip the v2v entries, then whole
+        rules by ``rule_degree``; inside a rule its own vertices come first, then the child that holds the index."""
+        count = self.v2v_p[node + 1] - self.v2v_p[node]
+        if index < count:
+            return int(self.v2v_c[self.v2v_p[node] + index])
+        index -= count
+        for rule in self.v2r_c[self.v2r_p[node]:self.v2r_p[node + 1]].tolist():
+            if index >= self.r_degree[rule]:
+                index -= int(self.r_degree[rule])
+                continue
+            while True:
+                own = self.r2v_p[rule + 1] - self.r2v_p[rule]
+                if index < own:
+                    return int(self.r2v_c[self.r2v_p[rule] + index])
+                index -= own
+                for child in self.children(rule):
+                    if index < self.r_degree[child]:
+                        rule = child
+                        break
+                    index -= int(self.r_degree[child])
+                else:
+                    raise IndexError("neighbour index out of range")
+        raise IndexError("neighbour index out of range")
+
+
+def neighbor_sample(v2v, v2r, r2v, r2r_levels, v_degree, r_degree, seeds, fanouts, seed=0, draw=None):
+    """``(samples, rows, cols)`` of neighbour sampling on a compressed graph, node by node as
+    neighbor_sample_sim_impl does it (ref: src/sample/csrc/neighbor_sample.h:27-131): a frontier node whose
+    degree does not exceed the fan-out contributes its whole neighbour list; any other node ``fanout``
+    distinct neighbour indices by Floyd's scheme (:97-121), each resolved by ``neighbor_at``.  New nodes get
+    local ids in the order they are first seen.  Random indices: ``draw(j, position, t, hop)`` uniform below
+    ``j``; by default Philox words counted by (frontier position, draw, hop) under ``seed``, mapped by
+    multiply-shift -- the generator of the device code; pass ``lambda j, *_: int(torch.randint(0, j, (1,)))``
+    to follow the reference's own draws."""
+    graph = CompressedNeighbors(v2v, v2r, r2v, r2r_levels, v_degree, r_degree)
+    if draw is None:
+        def draw(j, position, t, hop):
+            word = philox_first_word(position & 0xFFFFFFFF, (position >> 32) & 0xFFFFFFFF, t, hop, seed)
+            return (word * j) >> 32
+
+    samples = [int(s) for s in seeds]
+    local = {}
+    for i, s in enumerate(samples):
+        local.setdefault(s, i)
+    rows, cols = [], []
+    begin, end = 0, len(samples)
+    for hop, fanout in enumerate(fanouts):
+        for i in range(begin, end):
+            node = samples[i]
+            degree = int(v_degree[node])
+            if degree == 0:
+                continue
+            if fanout >= degree:
+                picks = graph.neighbor_list(node)
+            else:
+                drawn, picks = [], []
+                for t, j in enumerate(range(degree - fanout, degree)):
+                    index = draw(j, i, t, hop)
+                    if index in drawn:
+                        index = j
+                    drawn.append(index)
+                    picks.append(graph.neighbor_at(node, index))
+            for v in picks:
+                if v not in local:
+                    local[v] = len(samples)
+                    samples.append(v)
+                rows.append(i)
+                cols.append(local[v])
+        begin, end = end, len(samples)
+    return np.array(samples, np.int64), np.array(rows, np.int64), np.array(cols, np.int64)
