@@ -759,6 +759,76 @@ def measure_compress(name, steps, with_cpu=True):
     return report
 
 
+def measure_sample(name, batches, batch_size=1024, fanouts=(25, 10), with_cpu=True):
+    """Neighbour sampling on the compressed graph of a workload: mini-batches of `batch_size` seed nodes drawn
+    without replacement, two hops with the fan-outs GraphSAGE-style loaders use; CUDA events around `batches`
+    batches after three warm-up batches (host time around them as well: a batch ends with the host knowing
+    the sizes).  CPU baseline: the reference's own host sampler compiled from its sources (oracle/_ref) on
+    the same graph arrays and seeds, one thread (it has no parallel form), on a bounded number of batches."""
+    import torch
+    from compressgnn_b200.sample import CompressGraphSampler
+    from oracle import oracle
+    data, e_orig = build_graph(name)
+    graph = data.edge_index
+    host = None
+    if with_cpu:
+        host = [t.clone() for b in (graph.v2v_graph, graph.v2r_graph, graph.r2v_graph) for t in b.csr()[:2]]
+        host_levels = ([l.csr()[0].clone() for l in graph.r2r_graph], [l.csr()[1].clone() for l in graph.r2r_graph])
+        host_degrees = (graph.vertex_degree.clone(), graph.rule_degree.clone())
+    levels = graph.step
+    graph.to("cuda")
+    sampler = CompressGraphSampler.from_graph(graph)
+    gen = torch.Generator().manual_seed(11)
+    seeds = [torch.randperm(graph.vertex_cnt, generator=gen)[:batch_size] for _ in range(batches + 3)]
+    device_seeds = [s.cuda() for s in seeds]
+    edges = 0
+    for s in device_seeds[:3]:
+        sampler(s, fanouts, seed=1)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    start.record()
+    for i, s in enumerate(device_seeds[3:]):
+        edges += sampler(s, fanouts, seed=i)[1].numel()
+    stop.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    ms = start.elapsed_time(stop) / batches
+    report = {"metric": "sampled_edges_per_s", "value": edges / batches / ms / 1e3, "unit": "Medge/s", "ms_per_step": ms,
+              "host_ms_per_step": wall * 1e3 / batches, "steps": batches, "warmup": 3, "higher_is_better": True,
+              "dtype": "int64", "data": "synthetic",
+              "config": {"workload": f"sample: neighbour sampling on the compressed {name} graph", "nodes": graph.vertex_cnt,
+                         "orig_edges": e_orig, "rules": graph.rule_cnt, "levels": levels, "batch": batch_size,
+                         "fanouts": list(fanouts), "sampled_edges_per_batch": edges / batches}}
+    ref = oracle.reference_sample_module() if with_cpu else None
+    if with_cpu and ref is None:
+        report["cpu_baseline"] = {"value": None, "unit": "Medge/s", "cores": 0, "kind": "reference",
+                                  "sample": "unavailable: oracle/_ref/compressgnn_sample.so is not built on this box"}
+    elif with_cpu and levels > 1:
+        report["cpu_baseline"] = {"value": None, "unit": "Medge/s", "cores": 0, "kind": "reference",
+                                  "sample": "not run: the reference's sampler indexes the rule levels by descent depth and "
+                                            "does not follow rules nested more than one level deep"}
+    elif with_cpu:
+        n_cpu = min(batches, 8)
+        cpu_edges = 0
+        t0 = time.perf_counter()
+        for s in seeds[3:3 + n_cpu]:
+            cpu_edges += ref.neighbor_sample_cg_sim(*host, host_levels[0], host_levels[1], *host_degrees, s,
+                                                    list(fanouts))[1].numel()
+        cpu_sec = time.perf_counter() - t0
+        report["cpu_baseline"] = {"value": cpu_edges / cpu_sec / 1e6, "unit": "Medge/s", "cores": 1, "kind": "reference",
+                                  "ms_per_step": cpu_sec * 1e3 / n_cpu,
+                                  "sample": f"{n_cpu} of the {batches} batches, the reference's host sampler (one thread)"}
+    return report
+
+
+def run_sample(args):
+    import torch
+    torch.cuda.set_device(0)
+    report = measure_sample(args.graph, args.steps, with_cpu=not args.no_cpu_baseline)
+    print(json.dumps(dict(report, n_gpus=1, scaling="strong", vs_baseline=None, gpu_launches=None)))
+
+
 def run_compress(args):
     import torch
     torch.cuda.set_device(0)
@@ -983,10 +1053,11 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["cgnn", "reference"], default="cgnn")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cluster", "gcn", "compress"], default="propagation")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["cluster", "gcn", "compress", "sample"],
+                    default="propagation")
     ap.add_argument("--cluster-nodes", type=int, default=2450000)
     ap.add_argument("--graph", choices=sorted(WORKLOADS), default="propagation",
-                    help="graph of the compress workload")
+                    help="graph of the compress and sample workloads")
     ap.add_argument("--width", type=int, default=0,
                     help="feature columns of a propagation workload (default: the workload's own)")
     ap.add_argument("--scaling", choices=["strong", "weak"], default="strong",
@@ -1001,6 +1072,8 @@ def main():
     args = ap.parse_args()
     if args.workload == "compress":
         run_compress(args)
+    elif args.workload == "sample":
+        run_sample(args)
     elif args.workload == "cluster":
         run_cluster(args)
     elif args.workload == "gcn":
