@@ -19,8 +19,9 @@ ranks); `e2e` goes through the public host-buffer front end with pinned host mat
 is the reference's CPU spmm_func chain on this host's cores, and `parity_checked` compares the
 GPU's forward and backward results with that chain's on the same inputs.  `extra` carries short
 legs of the other operator groups: the cluster / reconstruct operators at 2.45 M nodes, the
-2-layer GCN epoch over four feature widths (sharded over the GPUs when N > 1), and the grammar
-compression of the workload's graph on the device beside the host compressor.
+2-layer GCN epoch over four feature widths (sharded over the GPUs when N > 1), the grammar
+compression of the workload's graph on the device beside the host compressor, and neighbour sampling
+on the compressed graph beside the reference's host sampler.
 """
 import argparse
 import json
@@ -497,6 +498,7 @@ def run_gpu(args):
     if not args.no_extra and WORKLOADS[args.workload]["n"] < 2_000_000:
         if world == 1:
             extra["compress"] = measure_compress(args.workload, 3, with_cpu=not args.no_cpu_baseline)
+            extra["sample"] = measure_sample(args.workload, 20, with_cpu=not args.no_cpu_baseline)
             extra["cluster"] = measure_cluster(args.cluster_nodes, max(3, min(args.steps, 10)), 3,
                                                with_cpu=not args.no_cpu_baseline)
         extra["gcn"] = measure_gcn(graph, e_orig, max(5, min(args.steps, 20)), 5, world, rank, device)
