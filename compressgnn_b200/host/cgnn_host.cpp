@@ -69,8 +69,9 @@ void splice_first(std::vector<int64_t> &list, int64_t id, const std::vector<int6
 // children (ref: mergeRule, src/offline/csrc/filter.h:31-67, depth_filter.h:17-40).
 template <typename ParentHook, typename ChildHook>
 void inline_rule(int64_t id, int64_t n, Rows &graph, Rows &graphT, ParentHook on_parent, ChildHook on_child) {
-    const std::vector<int64_t> body = graph[id];
-    const std::vector<int64_t> parents = graphT[id];
+    // neither list is spliced below (a rule is no parent or child of itself), so they are read in place
+    const std::vector<int64_t> &body = graph[id];
+    const std::vector<int64_t> &parents = graphT[id];
     for (int64_t node : parents) {
         splice_first(graph[node], id, body);
         on_parent(node, (int64_t)body.size());
@@ -92,6 +93,11 @@ void emit_filtered(const Rows &graph, const std::vector<char> &removed, int64_t 
         if (!removed[i]) ++cur;
     }
     std::vector<int64_t> vl{0}, el;
+    size_t kept = 0;
+    for (int64_t v = 0; v < n + r; ++v)
+        if (v < n || !removed[v - n]) kept += graph[v].size();
+    el.reserve(kept);
+    vl.reserve((size_t)(n + r) + 1);
     for (int64_t v = 0; v < n + r; ++v) {
         if (v >= n && removed[v - n]) continue;
         for (int64_t d : graph[v]) el.push_back(d >= n ? new_id[d - n] : d);
