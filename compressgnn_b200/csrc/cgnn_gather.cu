@@ -66,14 +66,28 @@ __device__ __forceinline__ uint4 philox4x32_7(uint64_t counter, uint64_t seed) {
     return make_uint4(c0, c1, c2, c3);
 }
 
-// Dropout of the VW values of the vector that starts at element `first` of the output (VW <= 4).
+// Dropout of the VW values of the vector that starts at element `first` of the output (VW is 1, 2 or 4 and
+// divides `first`).  Element e takes word e % 4 of the Philox block counted e / 4, so the mask is a
+// function of (seed, element index) alone: the same whatever the element type or the kernel that writes it.
 template <typename T, int VW>
 __device__ __forceinline__ void drop_vector(Vec<T, VW> &y, int64_t first, uint32_t threshold, T keep_scale,
                                             uint64_t seed) {
-    const uint4 r = philox4x32_7((uint64_t)first, seed);
-    const uint32_t word[4] = {r.x, r.y, r.z, r.w};
+    static_assert(VW == 1 || VW == 2 || VW == 4, "a vector lies inside one block of four random words");
+    const uint4 r = philox4x32_7((uint64_t)first >> 2, seed);
+    if constexpr (VW == 4) {
+        const uint32_t word[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-    for (int k = 0; k < VW; ++k) y.v[k] = word[k] < threshold ? T(0) : y.v[k] * keep_scale;
+        for (int k = 0; k < 4; ++k) y.v[k] = word[k] < threshold ? T(0) : y.v[k] * keep_scale;
+    } else if constexpr (VW == 2) {
+        const bool upper = (first & 2) != 0;
+        const uint32_t w0 = upper ? r.z : r.x, w1 = upper ? r.w : r.y;
+        y.v[0] = w0 < threshold ? T(0) : y.v[0] * keep_scale;
+        y.v[1] = w1 < threshold ? T(0) : y.v[1] * keep_scale;
+    } else {
+        const int at = (int)(first & 3);
+        const uint32_t w = at == 0 ? r.x : at == 1 ? r.y : at == 2 ? r.z : r.w;
+        y.v[0] = w < threshold ? T(0) : y.v[0] * keep_scale;
+    }
 }
 
 // A group of LPR lanes expands LPR consecutive node rows per step: lane l reads index[r0 + l]

@@ -233,8 +233,8 @@ int cgnn_cluster_reconstruct(int dtype, int64_t n, int64_t width, int64_t groups
  *   out[r,:] = dropout_p(relu(reps[index[r],:] + bias))
  * (ref: model/compressgnn/gcn.py:54-61 applies F.relu and F.dropout to the reconstructed [N,F]
  * matrix as two further elementwise passes.)  An element is dropped with probability drop_p, the
- * others are scaled by 1/(1-drop_p); the random words are Philox4x32 outputs counted by the
- * element's position under the key `seed`, so the mask depends on (seed, position) only.  The
+ * others are scaled by 1/(1-drop_p); element e of `out` takes word e % 4 of the Philox4x32 block
+ * counted e / 4 under the key `seed`, so the mask depends on (seed, element index) only.  The
  * backward pass needs no mask tensor: with ReLU in front, a dropped element and a clamped one both
  * read 0 in `out`, which cgnn_cluster_reconstruct_backward's exact-mask mode (relu = 1) turns into
  * a zero gradient; the caller multiplies the result by 1/(1-drop_p). */

@@ -310,6 +310,28 @@ def test_reconstruct_with_fused_dropout(width):
     torch.testing.assert_close(g_b, r_b, rtol=1e-4, atol=1e-2)
 
 
+@pytest.mark.parametrize("width", [6, 64, 130])
+def test_fused_dropout_in_double_precision(width):
+    """The same epilogue on fp64 rows (two values per 16-byte vector, and the scalar path at odd widths)."""
+    from compressgnn_b200 import runtime as rt
+    gen = torch.Generator(device="cuda").manual_seed(width)
+    n, groups, p = 5000, 40, 0.25
+    reps = torch.randn(groups, width, device="cuda", dtype=torch.float64, generator=gen)
+    bias = torch.randn(width, device="cuda", dtype=torch.float64, generator=gen)
+    index = torch.randint(0, groups, (n,), device="cuda", generator=gen)
+    plain = rt.cluster_reconstruct(reps, index, bias, True)
+    fused = rt.cluster_reconstruct(reps, index, bias, True, dropout_p=p, seed=77)
+    kept = fused != 0
+    torch.testing.assert_close(fused[kept], plain[kept] / (1 - p), rtol=1e-14, atol=0)
+    positive = plain > 0
+    rate = 1.0 - (kept & positive).sum().item() / positive.sum().item()
+    assert abs(rate - p) < 0.02, rate
+    # the mask depends on (seed, element position) only, not on the element type
+    single = rt.cluster_reconstruct(reps.float(), index, bias.float(), True, dropout_p=p, seed=77)
+    agree = ((single != 0) == kept) | (plain.abs() < 1e-6)
+    assert agree.all()
+
+
 def test_gcn_training_mode_uses_the_fused_dropout():
     from compressgnn_b200.model import GCN
     data = make_data(n=3000, width=32)
