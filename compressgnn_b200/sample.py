@@ -152,3 +152,19 @@ def neighbor_sample_cg_sim(v2v_vlist, v2v_elist, v2r_vlist, v2r_elist, r2v_vlist
     sampler = CompressGraphSampler(v2v_vlist, v2v_elist, v2r_vlist, v2r_elist, r2v_vlist, r2v_elist, r2r_vlist,
                                    r2r_elist, v_degree, r_degree)
     return sampler(input_node, num_neighbors, seed=seed)
+
+
+def neighbor_sample_ori_impl(colptr, row, input_node, num_neighbors, seed=None):
+    """The reference's sampler for an uncompressed graph in CSC form (``neighbor_sample_ori_impl``,
+    ``src/sample/csrc/neighbor_sample.h:134-212``): the same hops on a graph without rules.  As there,
+    the second result holds the local ids of the sampled neighbours and the third those of the frontier nodes."""
+    device = colptr.device
+    nodes = colptr.numel() - 1
+    none = torch.zeros(1, dtype=torch.int64, device=device)
+    empty = torch.empty(0, dtype=torch.int64, device=device)
+    degree = torch.diff(colptr.to(torch.int64))
+    sampler = CompressGraphSampler(colptr, row, torch.zeros(nodes + 1, dtype=torch.int64, device=device), empty,
+                                   none, empty, [], [], degree, empty)
+    samples, frontier, neighbours = sampler(input_node, num_neighbors, seed=seed)
+    return samples, neighbours, frontier
+

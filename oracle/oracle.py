@@ -454,3 +454,15 @@ def neighbor_sample(v2v, v2r, r2v, r2r_levels, v_degree, r_degree, seeds, fanout
                 cols.append(local[v])
         begin, end = end, len(samples)
     return np.array(samples, np.int64), np.array(rows, np.int64), np.array(cols, np.int64)
+
+
+def neighbor_sample_plain(colptr, row, seeds, fanouts, seed=0, draw=None):
+    """The uncompressed form (ref: neighbor_sample_ori_impl, src/sample/csrc/neighbor_sample.h:134-212): the
+    same loop on a graph without rules; returns ``(samples, neighbour local ids, frontier local ids)``."""
+    nodes = colptr.size - 1
+    zeros = np.zeros(nodes + 1, np.int64)
+    none = np.zeros(0, np.int64)
+    samples, frontier, neighbours = neighbor_sample((colptr, row), (zeros, none), (np.zeros(1, np.int64), none), [],
+                                                    np.diff(colptr), none, seeds, fanouts, seed=seed, draw=draw)
+    return samples, neighbours, frontier
+

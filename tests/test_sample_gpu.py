@@ -136,3 +136,18 @@ def test_a_seed_outside_the_graph_is_reported_not_followed(vectors):
     device_sample(g, np.array([3, 10 ** 6], np.int64), [2], 0)
     with pytest.raises(RuntimeError):
         rt.raise_on_device_status()
+
+
+def test_plain_graph_form(vectors):
+    """neighbor_sample_ori_impl: an uncompressed CSC graph, i.e. no rules at all."""
+    from compressgnn_b200 import runtime as rt
+    from compressgnn_b200.sample import neighbor_sample_ori_impl
+    colptr, row = vectors["b_v2v_ptr"], vectors["b_v2v_col"]
+    seeds = vectors["b_seeds"]
+    for trial, fanouts in enumerate(([3, 3], [1000, 1], [1, 1, 1])):
+        got = neighbor_sample_ori_impl(cu(colptr), cu(row), cu(seeds), fanouts, seed=trial)
+        want = oracle.neighbor_sample_plain(colptr, row, seeds, fanouts, seed=trial)
+        for mine, theirs in zip(got, want):
+            np.testing.assert_array_equal(mine.cpu().numpy(), theirs)
+    rt.raise_on_device_status()
+

@@ -88,3 +88,20 @@ def test_index_order_and_list_order_cover_the_same_neighbours(vectors):
         assert len(listed) == int(v_degree[node])
         assert sorted(listed) == sorted(graph.neighbor_at(node, i) for i in range(len(listed)))
         assert sorted(listed) == sorted(incoming[node])
+
+
+def test_plain_graph_form_against_the_compiled_reference(vectors):
+    ref = oracle.reference_sample_module()
+    if ref is None:
+        pytest.skip("oracle/_ref/compressgnn_sample.so is not built here")
+    colptr, row = vectors["a_v2v_ptr"], vectors["a_v2v_col"]   # any CSR serves as an uncompressed graph
+    seeds = vectors["a_seeds"][:4]
+    for trial, fanouts in enumerate(([2, 2], [1000], [1, 3])):
+        torch.manual_seed(40 + trial)
+        want = ref.neighbor_sample_ori_impl(torch.from_numpy(colptr), torch.from_numpy(row), torch.from_numpy(seeds),
+                                            list(fanouts))
+        torch.manual_seed(40 + trial)
+        got = oracle.neighbor_sample_plain(colptr, row, seeds, fanouts, draw=lambda j, *_: int(torch.randint(0, j, (1,))))
+        for mine, theirs in zip(got, want):
+            np.testing.assert_array_equal(mine, theirs.numpy())
+
