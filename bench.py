@@ -669,6 +669,9 @@ def measure_cluster(n, steps, warmup, with_cpu=True):
                                   4 * groups * width + 8 * n + 4 * n * width),
         "cluster_reconstruct (bias+relu)": (lambda: rt.cluster_reconstruct(table, ids, bias, True),
                                             4 * groups * out_width + 8 * n + 4 * out_width + 4 * n * out_width),
+        "cluster_reconstruct (bias+relu+dropout 0.3)": (
+            lambda: rt.cluster_reconstruct(table, ids, bias, True, dropout_p=0.3, seed=5),
+            4 * groups * out_width + 8 * n + 4 * out_width + 4 * n * out_width),
         "cluster_reconstruct_backward (relu, exact mask)": (
             lambda: rt.cluster_reconstruct_backward(grad_out, ids, y, groups, True),
             8 * n * out_width + 8 * n + 4 * groups * out_width),
