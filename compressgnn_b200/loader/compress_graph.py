@@ -104,6 +104,7 @@ class CompressGraph:
         self.vertex_degree = self.vertex_degree.to(device)
         self.rule_degree = self.rule_degree.to(device)
         self._plan = None
+        self._sampler = None
         return self
 
     def blocks(self):
@@ -111,6 +112,14 @@ class CompressGraph:
 
     def edge_count(self):
         return sum(b.nnz() for b in self.blocks())
+
+    def neighbor_sampler(self):
+        """The neighbour sampler of this graph on its CUDA device (``compressgnn_b200.sample``), built on
+        first use: merged rule table, exact degrees, per-vertex tables."""
+        if getattr(self, "_sampler", None) is None or self._sampler.device != self.v2v_graph.device:
+            from ..sample import CompressGraphSampler
+            self._sampler = CompressGraphSampler.from_graph(self)
+        return self._sampler
 
     def propagation_plan(self):
         if self._plan is None:

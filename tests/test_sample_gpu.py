@@ -76,7 +76,8 @@ def test_nested_rules_and_the_sampler_object():
     blocks = (blk(graph.v2v_graph), blk(graph.v2r_graph), blk(graph.r2v_graph), [blk(l) for l in graph.r2r_graph])
     v_degree, r_degree = oracle.exact_degrees(*blocks)
     graph.to("cuda")
-    sampler = CompressGraphSampler.from_graph(graph)
+    sampler = graph.neighbor_sampler()
+    assert isinstance(sampler, CompressGraphSampler) and graph.neighbor_sampler() is sampler
     np.testing.assert_array_equal(sampler._arrays[8].cpu().numpy(), v_degree)
     np.testing.assert_array_equal(sampler._arrays[9].cpu().numpy(), r_degree)
     rng = np.random.default_rng(1)
