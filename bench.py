@@ -632,13 +632,17 @@ def measure_cluster(n, steps, warmup, with_cpu=True):
     cluster.refresh_count = 0
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
     with ClockSampler(torch.cuda.current_device()) as clocks:
         start.record()
+        marks[0].record()
         for e in range(steps):
             epoch(e)
+            marks[e + 1].record()
         stop.record()
         torch.cuda.synchronize()
     ms_epoch = start.elapsed_time(stop) / steps
+    each = sorted(a.elapsed_time(b) for a, b in zip(marks, marks[1:]))  # a stalled epoch shows as max >> median
 
     # per-operator timings on the same tensors (CUDA events, median of 20)
     def timed(fn, reps_=20):
@@ -705,7 +709,8 @@ def measure_cluster(n, steps, warmup, with_cpu=True):
     # the operator that moves the most bytes per epoch is the roofline's subject
     dom = "cluster_reconstruct (bias+relu)"
     report = {"metric": "cluster_linear_reconstruct_nodes_per_s", "value": n / (ms_epoch * 1e-3) / 1e6, "unit": "Mnode/s",
-              "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms_epoch, "higher_is_better": True,
+              "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms_epoch, "ms_per_step_median": each[len(each) // 2],
+              "ms_per_step_max": each[-1], "higher_is_better": True,
               "dtype": "f32", "data": "synthetic",
               "config": {"workload": "cluster: Compressgnn_Cluster + Linear 128->256 + Compressgnn_Reconstruct(relu), fwd+bwd",
                          "nodes": n, "feature_width": width, "out_width": out_width, "bits": bits, "centroids": 4096,
@@ -967,19 +972,24 @@ def measure_gcn(graph, e_orig, steps, warmup, world, rank, device, widths=(16, 6
             dist.barrier()
             torch.cuda.synchronize()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
         start.record()
+        marks[0].record()
         for e in range(steps):
             loss = epoch(e)
+            marks[e + 1].record()
         stop.record()
         torch.cuda.synchronize()
         ms = start.elapsed_time(stop) / steps
+        each = sorted(a.elapsed_time(b) for a, b in zip(marks, marks[1:]))
         if world > 1:
             t = torch.tensor([ms], device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         if sharded:
             net.consolidate_parameters()
-        report[str(width)] = {"epoch_ms": ms, "final_loss": float(loss.detach()),
+        report[str(width)] = {"epoch_ms": ms, "epoch_ms_median": each[len(each) // 2], "epoch_ms_max": each[-1],
+                              "final_loss": float(loss.detach()),
                               "placement": "columns sharded" if sharded else ("replica per GPU" if world > 1 else "one GPU")}
         del model, net, opt, x
     rt.raise_on_device_status()
