@@ -633,6 +633,7 @@ def measure_cluster(n, steps, warmup, with_cpu=True):
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    plans_before = rt.SegmentPlan.built_from_index
     with ClockSampler(torch.cuda.current_device()) as clocks:
         start.record()
         marks[0].record()
@@ -641,6 +642,7 @@ def measure_cluster(n, steps, warmup, with_cpu=True):
             marks[e + 1].record()
         stop.record()
         torch.cuda.synchronize()
+    plans_sorted = rt.SegmentPlan.built_from_index - plans_before  # 0: every refresh handed its plan over
     ms_epoch = start.elapsed_time(stop) / steps
     each = sorted(a.elapsed_time(b) for a, b in zip(marks, marks[1:]))  # a stalled epoch shows as max >> median
 
@@ -710,7 +712,7 @@ def measure_cluster(n, steps, warmup, with_cpu=True):
     dom = "cluster_reconstruct (bias+relu)"
     report = {"metric": "cluster_linear_reconstruct_nodes_per_s", "value": n / (ms_epoch * 1e-3) / 1e6, "unit": "Mnode/s",
               "steps": steps, "warmup": max(warmup, 3), "ms_per_step": ms_epoch, "ms_per_step_median": each[len(each) // 2],
-              "ms_per_step_max": each[-1], "higher_is_better": True,
+              "ms_per_step_max": each[-1], "index_plans_rebuilt_in_timed_region": plans_sorted, "higher_is_better": True,
               "dtype": "f32", "data": "synthetic",
               "config": {"workload": "cluster: Compressgnn_Cluster + Linear 128->256 + Compressgnn_Reconstruct(relu), fwd+bwd",
                          "nodes": n, "feature_width": width, "out_width": out_width, "bits": bits, "centroids": 4096,

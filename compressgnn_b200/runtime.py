@@ -135,11 +135,14 @@ class SegmentPlan:
                 col1.numel() if col1 is not None else 0, int(split), _stream_ptr(device)))
         return cls(handle.value, device)
 
+    built_from_index = 0  # plans built by a sort of the index (the path an assignment refresh does not take)
+
     @classmethod
     def from_index(cls, index, groups, split=0):
         """Plan that groups the positions of ``index`` by value (``groups`` segments)."""
         _require(index.is_cuda and index.dtype == torch.int64 and index.dim() == 1 and
                  index.is_contiguous(), "Expected contiguous int64 index on input device")
+        SegmentPlan.built_from_index += 1
         handle = ctypes.c_void_p(0)
         with on_device(index.device):
             check(lib().cgnn_plan_create_from_index(ctypes.byref(handle), _ptr(index), index.numel(),
