@@ -267,6 +267,51 @@ static int launch_expand(const ExpandArgs<T> &a, cudaStream_t stream) {
     return CGNN_OK;
 }
 
+// Rows whose byte length is no multiple of 16 (47 class scores: 188 bytes): the output is written as ONE
+// flat array in aligned 16-byte vectors, a vector taking its elements from up to two node rows.  The
+// table rows it reads are few and stay in cache; what matters is that every store is a whole aligned vector
+// instead of one element per lane with rows starting at odd offsets.
+template <typename T>
+__global__ void __launch_bounds__(256) expand_flat_kernel(const ExpandArgs<T> a) {
+    constexpr int VW = 16 / (int)sizeof(T);
+    using V = Vec<T, VW>;
+    const int64_t total = a.n * a.width, vectors = total / VW;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < vectors; i += (int64_t)blockDim.x * gridDim.x) {
+        const int64_t first = i * VW;
+        int64_t r = first / a.width;
+        int64_t c = first - r * a.width;
+        V y;
+#pragma unroll
+        for (int k = 0; k < VW; ++k) {
+            const int64_t g = a.index[r];
+            T v = T(0);
+            if (g < 0 || g >= a.groups) atomicOr(&g_gather_status, STATUS_BAD_INDEX);
+            else v = a.table[g * a.width + c];
+            if (a.bias) v += a.bias[c];
+            y.v[k] = (a.relu && v < T(0)) ? T(0) : v;
+            if (++c == a.width) {
+                c = 0;
+                ++r;
+            }
+        }
+        if (a.drop_threshold) drop_vector<T, VW>(y, first, a.drop_threshold, a.keep_scale, a.seed);
+        vec_store_cs<T, VW>(a.out + first, y);
+    }
+    // the last total % VW elements
+    if (blockIdx.x == 0 && threadIdx.x < total - vectors * VW) {
+        const int64_t e = vectors * VW + threadIdx.x, r = e / a.width, c = e - r * a.width;
+        const int64_t g = a.index[r];
+        T v = T(0);
+        if (g < 0 || g >= a.groups) atomicOr(&g_gather_status, STATUS_BAD_INDEX);
+        else v = a.table[g * a.width + c];
+        if (a.bias) v += a.bias[c];
+        Vec<T, 1> y;
+        y.v[0] = (a.relu && v < T(0)) ? T(0) : v;
+        if (a.drop_threshold) drop_vector<T, 1>(y, e, a.drop_threshold, a.keep_scale, a.seed);
+        a.out[e] = y.v[0];
+    }
+}
+
 template <typename T>
 static int expand_typed(const ExpandArgs<T> &a, cudaStream_t stream) {
     constexpr int VWMAX = 16 / (int)sizeof(T);
@@ -285,6 +330,13 @@ static int expand_typed(const ExpandArgs<T> &a, cudaStream_t stream) {
         if (vecs <= 8) return launch_expand<T, VWMAX, 8>(a, stream);
         if (vecs <= 16) return launch_expand<T, VWMAX, 16>(a, stream);
         return launch_expand<T, VWMAX, 32>(a, stream);
+    }
+    if (a.div_counts == nullptr && aligned16(a.out) && a.width > 4) {
+        const int64_t vectors = a.n * a.width / VWMAX;
+        const int64_t blocks = std::max<int64_t>(1, std::min<int64_t>(ceil_div(vectors, 256), 148 * 16));
+        expand_flat_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(a);
+        CGNN_LAUNCH_CHECK();
+        return CGNN_OK;
     }
     if (a.width <= 4) return launch_expand<T, 1, 4>(a, stream);
     if (a.width <= 8) return launch_expand<T, 1, 8>(a, stream);
