@@ -58,7 +58,11 @@ def exact_degrees(v2v_vlist, v2r_vlist, v2r_elist, r2v_vlist, r2r_vlist, r2r_eli
 
 
 class CompressGraphSampler:
-    """Sampler bound to one compressed graph on one CUDA device; ``sampler(input_node, num_neighbors)``."""
+    """Sampler bound to one compressed graph on one CUDA device; ``sampler(input_node, num_neighbors)``.
+
+    The object owns two per-vertex tables that a call fills and clears again, so calls on one sampler must
+    not overlap (one call at a time; use one sampler per stream or worker).  A fan-out of 0 or less samples
+    nothing at that hop, as in the reference."""
 
     def __init__(self, v2v_vlist, v2v_elist, v2r_vlist, v2r_elist, r2v_vlist, r2v_elist, r2r_vlist, r2r_elist,
                  v_degree, r_degree):
