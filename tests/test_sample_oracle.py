@@ -105,3 +105,25 @@ def test_plain_graph_form_against_the_compiled_reference(vectors):
         for mine, theirs in zip(got, want):
             np.testing.assert_array_equal(mine, theirs.numpy())
 
+
+def test_host_side_of_the_device_sampler(vectors):
+    """The two pieces of compressgnn_b200.sample that are plain tensor code: one rule -> rule CSR out of the
+    level blocks, and the exact degrees (against the oracle's, and against the reference's gen_degree arrays
+    on a graph of one level, where the two agree)."""
+    from compressgnn_b200.sample import exact_degrees, merge_rule_levels
+    g = graph_of(vectors, "a")
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a))
+    rules = g["r_degree"].size
+    ptr, col = merge_rule_levels([t(l[0]) for l in g["r2r_levels"]], [t(l[1]) for l in g["r2r_levels"]], rules,
+                                 torch.device("cpu"))
+    lists = oracle.CompressedNeighbors(**g)
+    for rule in range(rules):
+        assert col[ptr[rule]:ptr[rule + 1]].tolist() == lists.children(rule)
+    v_degree, r_degree = exact_degrees(t(g["v2v"][0]), t(g["v2r"][0]), t(g["v2r"][1]), t(g["r2v"][0]),
+                                       [t(l[0]) for l in g["r2r_levels"]], [t(l[1]) for l in g["r2r_levels"]])
+    want_v, want_r = oracle.exact_degrees(g["v2v"], g["v2r"], g["r2v"], g["r2r_levels"])
+    np.testing.assert_array_equal(v_degree.numpy(), want_v)
+    np.testing.assert_array_equal(r_degree.numpy(), want_r)
+    np.testing.assert_array_equal(want_v, g["v_degree"])   # one level: gen_degree's arrays are exact
+    np.testing.assert_array_equal(want_r, g["r_degree"])
+
