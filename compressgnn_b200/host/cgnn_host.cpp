@@ -41,6 +41,7 @@ using Rows = std::vector<std::vector<int64_t>>;
 
 Rows rows_from_csr(const int64_t *vlist, const int64_t *elist, int64_t total) {
     Rows g((size_t)total);
+#pragma omp parallel for schedule(static)
     for (int64_t v = 0; v < total; ++v) g[v].assign(elist + vlist[v], elist + vlist[v + 1]);
     return g;
 }
@@ -51,6 +52,16 @@ Rows rows_from_csr(const int64_t *vlist, const int64_t *elist, int64_t total) {
 // hubs in thousands of rows those splices were most of the run time, so they are not kept here.
 Rows referencing_rows(const int64_t *vlist, const int64_t *elist, int64_t total, int64_t n) {
     Rows t((size_t)total);
+    std::vector<int32_t> uses((size_t)(total - n), 0);  // exact capacities first: no list is reallocated while it fills
+    const int64_t edges = vlist[total];
+#pragma omp parallel for schedule(static)
+    for (int64_t e = 0; e < edges; ++e)
+        if (elist[e] >= n) {
+#pragma omp atomic
+            ++uses[(size_t)(elist[e] - n)];
+        }
+#pragma omp parallel for schedule(static)
+    for (int64_t x = n; x < total; ++x) t[x].reserve((size_t)uses[(size_t)(x - n)]);
     for (int64_t v = 0; v < total; ++v)
         for (int64_t e = vlist[v]; e < vlist[v + 1]; ++e)
             if (elist[e] >= n) t[elist[e]].push_back(v);
@@ -92,16 +103,18 @@ void emit_filtered(const Rows &graph, const std::vector<char> &removed, int64_t 
         new_id[i] = cur;
         if (!removed[i]) ++cur;
     }
-    std::vector<int64_t> vl{0}, el;
-    size_t kept = 0;
+    // row pointers of the surviving rows first, then every row copied to its place in parallel
+    std::vector<int64_t> keep;
+    keep.reserve((size_t)(n + r));
     for (int64_t v = 0; v < n + r; ++v)
-        if (v < n || !removed[v - n]) kept += graph[v].size();
-    el.reserve(kept);
-    vl.reserve((size_t)(n + r) + 1);
-    for (int64_t v = 0; v < n + r; ++v) {
-        if (v >= n && removed[v - n]) continue;
-        for (int64_t d : graph[v]) el.push_back(d >= n ? new_id[d - n] : d);
-        vl.push_back((int64_t)el.size());
+        if (v < n || !removed[v - n]) keep.push_back(v);
+    std::vector<int64_t> vl(keep.size() + 1, 0);
+    for (size_t i = 0; i < keep.size(); ++i) vl[i + 1] = vl[i] + (int64_t)graph[keep[i]].size();
+    std::vector<int64_t> el((size_t)vl.back());
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < (int64_t)keep.size(); ++i) {
+        int64_t at = vl[(size_t)i];
+        for (int64_t d : graph[keep[(size_t)i]]) el[(size_t)at++] = d >= n ? new_id[d - n] : d;
     }
     res->i64 = {std::move(vl), std::move(el)};
     res->scalars[0] = n;
