@@ -182,15 +182,23 @@ CGNN_HOST_API void cgnn_host_result_free(Result *r) { delete r; }
 CGNN_HOST_API int cgnn_host_add_self_loop_csr(const int64_t *vlist, const int64_t *elist, int64_t n,
                                               Result **out) {
     auto *res = new Result();
-    std::vector<int64_t> vl{0}, el;
-    el.reserve((size_t)(vlist[n] + n));
+    // which rows lack the loop (rows are independent), the new row pointers, then every row copied in parallel
+    std::vector<int64_t> vl((size_t)n + 1, 0);
+#pragma omp parallel for schedule(static)
     for (int64_t v = 0; v < n; ++v) {
-        int64_t e = vlist[v];
+        const int64_t *begin = elist + vlist[v], *end = elist + vlist[v + 1];
+        const int64_t *at = std::lower_bound(begin, end, v);  // rows are sorted
+        vl[(size_t)v + 1] = (end - begin) + ((at == end || *at != v) ? 1 : 0);
+    }
+    for (int64_t v = 0; v < n; ++v) vl[(size_t)v + 1] += vl[(size_t)v];
+    std::vector<int64_t> el((size_t)vl[(size_t)n]);
+#pragma omp parallel for schedule(static)
+    for (int64_t v = 0; v < n; ++v) {
+        int64_t e = vlist[v], o = vl[(size_t)v];
         const int64_t end = vlist[v + 1];
-        for (; e < end && elist[e] < v; ++e) el.push_back(elist[e]);
-        if (e == end || elist[e] != v) el.push_back(v);
-        for (; e < end; ++e) el.push_back(elist[e]);
-        vl.push_back((int64_t)el.size());
+        for (; e < end && elist[e] < v; ++e) el[(size_t)o++] = elist[e];
+        if (e == end || elist[e] != v) el[(size_t)o++] = v;
+        for (; e < end; ++e) el[(size_t)o++] = elist[e];
     }
     res->i64 = {std::move(vl), std::move(el)};
     *out = res;
@@ -200,12 +208,26 @@ CGNN_HOST_API int cgnn_host_add_self_loop_csr(const int64_t *vlist, const int64_
 // 1/sqrt(1e-6 + in-degree), accumulated in fp32 (ref: get_norm_degree,
 // src/offline/csrc/norm.h:20-45; INF is 1e-6 in util.h:16).
 CGNN_HOST_API int cgnn_host_get_norm_degree(const int64_t *dst, int64_t edges, int64_t n, float *out) {
-    for (int64_t v = 0; v < n; ++v) out[v] = 1e-6;
+    // The reference adds 1.0f to 1e-6f once per incoming edge, in fp32: the result depends on the number of
+    // additions only, so the edges are counted in parallel and every vertex repeats its own additions.
+    std::vector<int32_t> count((size_t)n, 0);
+    bool bad = false;
+#pragma omp parallel for schedule(static) reduction(|| : bad)
     for (int64_t e = 0; e < edges; ++e) {
-        if (dst[e] < 0 || dst[e] >= n) return fail("get_norm_degree: destination out of range");
-        out[dst[e]] += 1;
+        if (dst[e] < 0 || dst[e] >= n) {
+            bad = true;
+        } else {
+#pragma omp atomic
+            ++count[(size_t)dst[e]];
+        }
     }
-    for (int64_t v = 0; v < n; ++v) out[v] = 1 / std::sqrt(out[v]);
+    if (bad) return fail("get_norm_degree: destination out of range");
+#pragma omp parallel for schedule(dynamic, 4096)
+    for (int64_t v = 0; v < n; ++v) {
+        float sum = 1e-6;
+        for (int32_t k = 0; k < count[(size_t)v]; ++k) sum += 1;
+        out[v] = 1 / std::sqrt(sum);
+    }
     return 0;
 }
 
